@@ -100,6 +100,14 @@ _SIGNATURES = {
     "pl_moe_sort": [_PTR, _I32, _I32, _PTR, _PTR, _PTR, _PTR],
     "pl_moe_gather": [_PTR, _I64, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
     "pl_moe_combine": [_PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
+    "pl_add_layernorm": [_PTR, _PTR, _PTR, _PTR, _F32, _PTR, _PTR, _PTR, _F32, _PTR, _I32, _I32, _I32, _I32, _PTR],
+    "pl_gated_act": [_PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
+    "pl_sigmoid_gate": [_PTR, _I64, _PTR, _I64, _I32, _I32, _I32, _PTR],
+    "pl_conv_norm_rope_write": [_PTR, _I64, _PTR, _PTR, _I32, _PTR, _PTR, _I32, _PTR, _PTR, _F32, _PTR, _I32, _I32, _F32,
+                                _PTR, _PTR, _PTR, _I32, _PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _I32, _I32, _I32,
+                                _I32, _I32, _PTR, _PTR],
+    "pl_latent_rope_write": [_PTR, _I64, _I32, _I32, _PTR, _I64, _PTR, _I64, _PTR, _F32, _I32, _I32, _PTR, _I32, _F32,
+                             _PTR, _PTR, _PTR, _I32, _PTR, _I64, _I32, _I32, _I32, _I32, _PTR, _PTR],
     "pl_sample": [_PTR, _I64, _I32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR],
 }
 
@@ -590,6 +598,125 @@ def norm_write_paged(z: torch.Tensor, weight: torch.Tensor, eps: float, pos: tor
     _call("pl_norm_write_paged", _p(z), z.stride(0), _p(weight), float(eps), _p(pos), _p(entry), _p(table),
           table.shape[1], _p(pool), pool.stride(0), page_size, pool.shape[0], rank, tokens, _code(z.dtype),
           _p(status), _stream())
+
+
+def add_layernorm(x: torch.Tensor, y: torch.Tensor | None, y_weight: torch.Tensor | None,
+                  y_bias: torch.Tensor | None, y_eps: float, out: torch.Tensor | None,
+                  weight: torch.Tensor | None = None, bias: torch.Tensor | None = None, eps: float = 0.0,
+                  rows: torch.Tensor | None = None) -> None:
+    """x fp32 [T, H] += layernorm(y) * y_weight + y_bias (in place unless rows is given; nothing when
+    y is None); then out = the stream rounded to the engine's dtype, or with weight and bias its
+    layer norm. y and out in the engine's dtype, weights and biases fp32. With rows (int32 [R]),
+    output row r is made from source row rows[r] and x is left as it was."""
+    _dev(x, y, y_weight, y_bias, out, weight, bias, rows)
+    hidden = x.shape[-1]
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    dtype = out.dtype if out is not None else y.dtype
+    if y is not None:
+        assert y.shape == x.shape and y.is_contiguous() and y.dtype == dtype
+        for v in (y_weight, y_bias):
+            assert v.dtype == torch.float32 and v.shape == (hidden,) and v.is_contiguous()
+    n_rows = rows.numel() if rows is not None else x.shape[0]
+    if out is not None:
+        assert out.shape == (n_rows, hidden) and out.is_contiguous()
+    if weight is not None:
+        for v in (weight, bias):
+            assert v.dtype == torch.float32 and v.shape == (hidden,) and v.is_contiguous()
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.is_contiguous()
+    _call("pl_add_layernorm", _p(x), _p(y), _p(y_weight), _p(y_bias), float(y_eps), _p(out), _p(weight), _p(bias),
+          float(eps), _p(rows), n_rows, hidden, int(weight is not None), _code(dtype), _stream())
+
+
+GATED_ACT = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: str) -> None:
+    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]; act "silu" or "gelu_tanh" (the tanh form)."""
+    _dev(gate_up, out)
+    tokens, two_i = gate_up.shape
+    assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2) and out.dtype == gate_up.dtype
+    assert gate_up.is_contiguous() and out.is_contiguous()
+    _call("pl_gated_act", _p(gate_up), _p(out), tokens, two_i // 2, GATED_ACT[act], _code(out.dtype), _stream())
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x[t, i] *= sigmoid(gate[t, i]) in place; both [T, W] with free row strides (columns of wider matrices)."""
+    _dev(x, gate)
+    tokens, width = x.shape
+    assert gate.shape == x.shape and gate.dtype == x.dtype and x.stride(1) == 1 and gate.stride(1) == 1
+    _call("pl_sigmoid_gate", _p(x), x.stride(0) if tokens > 1 else width, _p(gate),
+          gate.stride(0) if tokens > 1 else width, tokens, width, _code(x.dtype), _stream())
+
+
+def conv_norm_rope_write(proj: torch.Tensor, bias: torch.Tensor | None, conv_weight: torch.Tensor | None,
+                         conv_state: torch.Tensor | None, slots: torch.Tensor | None, update_state: bool,
+                         q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float,
+                         inv_freq: torch.Tensor | None, rotary: int, interleaved: bool, amplitude: float,
+                         pos: torch.Tensor, entry: torch.Tensor, table: torch.Tensor, q_out: torch.Tensor,
+                         k_pool: torch.Tensor, v_pool: torch.Tensor, page_size: int, n_heads: int, n_kv: int,
+                         head_dim: int, status: torch.Tensor | None = None) -> None:
+    """From a token's projected q and k channels (proj [T, (n_heads + n_kv) * head_dim], columns of a
+    wider matrix allowed) to the rotated query rows q_out [T, n_heads * head_dim] and the token's
+    page: bias, causal convolution over time (conv_weight fp32 [channels, taps], conv_state [slots,
+    taps - 1, channels] the projected rows before this step's), one RMS norm over all q channels and
+    one over all k channels (q_norm, k_norm fp32), rotation of the first `rotary` columns of every
+    head (interleaved: neighbouring pairs; else halves), K page <- rotated normed key, V page <- the
+    filtered key before norm and rotation. update_state: every entry brings one token and its slot
+    moves on in the same launch."""
+    _dev(proj, bias, conv_weight, conv_state, slots, q_norm, k_norm, inv_freq, pos, entry, table, q_out, k_pool,
+         v_pool, status)
+    tokens, channels = proj.shape
+    q_width, k_width = n_heads * head_dim, n_kv * head_dim
+    assert channels == q_width + k_width and proj.stride(1) == 1 and q_out.shape == (tokens, q_width)
+    assert q_out.stride(1) == 1 and q_out.dtype == proj.dtype == k_pool.dtype == v_pool.dtype
+    taps = 1
+    if conv_weight is not None:
+        taps = conv_weight.shape[1]
+        assert conv_weight.dtype == torch.float32 and conv_weight.shape == (channels, taps) and conv_weight.is_contiguous()
+    if taps > 1:
+        assert conv_state.dtype == proj.dtype and conv_state.is_contiguous() and conv_state.shape[1:] == (taps - 1, channels)
+        assert slots.dtype == torch.int32
+    for v, n in ((bias, channels), (q_norm, q_width), (k_norm, k_width)):
+        assert v is None or (v.dtype == torch.float32 and v.shape == (n,) and v.is_contiguous())
+    if rotary:
+        assert inv_freq.dtype == torch.float64 and inv_freq.numel() == rotary // 2 and inv_freq.is_contiguous()
+    n_pages = k_pool.shape[0]
+    assert k_pool.shape == (n_pages, n_kv, page_size, head_dim) == v_pool.shape and k_pool.stride() == v_pool.stride()
+    assert k_pool.stride(3) == 1 and k_pool.stride(2) == head_dim and table.dim() == 2 and table.is_contiguous()
+    assert pos.dtype == torch.int32 and entry.dtype == torch.int32 and table.dtype == torch.int32
+    _call("pl_conv_norm_rope_write", _p(proj), proj.stride(0) if tokens > 1 else channels, _p(bias), _p(conv_weight),
+          taps, _p(conv_state) if taps > 1 else None, _p(slots), int(bool(update_state)), _p(q_norm), _p(k_norm),
+          float(eps), _p(inv_freq), int(rotary), int(bool(interleaved)), float(amplitude), _p(pos), _p(entry),
+          _p(table), table.shape[1], _p(q_out), q_out.stride(0) if tokens > 1 else q_width, _p(k_pool), _p(v_pool),
+          k_pool.stride(0), k_pool.stride(1), page_size, n_pages, tokens, n_heads, n_kv, head_dim,
+          _code(proj.dtype), _p(status), _stream())
+
+
+def latent_rope_write(q: torch.Tensor, q_out: torch.Tensor, z: torch.Tensor | None, weight: torch.Tensor | None,
+                      eps: float, rank: int, rot: int, inv_freq: torch.Tensor | None, interleaved: bool,
+                      amplitude: float, pos: torch.Tensor, entry: torch.Tensor, table: torch.Tensor,
+                      pool: torch.Tensor, page_size: int, status: torch.Tensor | None = None) -> None:
+    """The rows a latent-attention layer with a rotated key part caches, and the rotated part of its
+    queries. q [T, nh, dim + rot] (the last rot columns of every head are rotated into q_out [T, nh,
+    rank + rot] at columns rank...); z [T, rank + rot] (row stride free; None: nothing is cached):
+    pool row <- [rmsnorm(z[:rank]) * weight | rotate(z[rank:])]; pool [pages, 1, page_size, rank + rot]."""
+    _dev(q, q_out, z, weight, inv_freq, pos, entry, table, pool, status)
+    tokens, n_heads, q_row = q.shape
+    dim = q_row - rot
+    assert dim >= 0 and q.stride(2) == 1 and q.stride(1) == q_row and q_out.shape == (tokens, n_heads, rank + rot)
+    assert q_out.stride(2) == 1 and q_out.stride(1) == rank + rot and q_out.dtype == q.dtype == pool.dtype
+    if z is not None:
+        assert z.shape == (tokens, rank + rot) and z.stride(1) == 1 and z.dtype == q.dtype
+        assert weight.dtype == torch.float32 and weight.shape == (rank,) and weight.is_contiguous()
+    if rot:
+        assert inv_freq.dtype == torch.float64 and inv_freq.numel() == rot // 2 and inv_freq.is_contiguous()
+    assert pool.shape[1:] == (1, page_size, rank + rot) and pool.stride(3) == 1 and pool.stride(2) == rank + rot
+    assert table.dim() == 2 and table.is_contiguous() and table.dtype == torch.int32
+    _call("pl_latent_rope_write", _p(q), q.stride(0), n_heads, dim, _p(q_out), q_out.stride(0), _p(z),
+          z.stride(0) if z is not None else 0, _p(weight), float(eps), rank, rot, _p(inv_freq),
+          int(bool(interleaved)), float(amplitude), _p(pos), _p(entry), _p(table), table.shape[1], _p(pool),
+          pool.stride(0), page_size, pool.shape[0], tokens, _code(q.dtype), _p(status), _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:

@@ -211,8 +211,10 @@ class Attention(Part):
     this layer reads; it then has no k and v projections and writes nothing),
     softcap (optional: scaled scores pass through softcap * tanh(s / softcap) before
     the softmax; such a layer attends on the CUDA-core kernel, the only one that
-    squashes scores), qk_norm_eps (with the q_norm / k_norm tensors: eps of the
-    per-head RMS norm applied to q and k before the position encoding).
+    squashes scores), sink_logit (optional number s: one more term exp(s) joins every
+    head's softmax denominator, with no key and no value), qk_norm_eps (with the q_norm /
+    k_norm tensors: eps of the per-head RMS norm applied to q and k before the position
+    encoding).
     tensors: q [nh*hd, H], k and v [nkv*hd, H], o [H, nh*hd]; optional q_norm and
     k_norm [hd] (kept in float32). q, k and v are stacked into one operand at load.
     """
@@ -231,6 +233,9 @@ class Attention(Part):
         self.cache_from = p.get("cache_from")
         self.softcap = float(p["softcap"]) if p.get("softcap") else 0.0
         self.qk_norm_eps = float(p.get("qk_norm_eps") or 0.0)
+        self.sink_logit = float(p["sink_logit"]) if p.get("sink_logit") is not None else None
+        self.sinks = (torch.full((self.n_heads,), self.sink_logit, dtype=torch.float32, device=ctx.device)
+                      if self.sink_logit is not None else None)
         self.q_norm: torch.Tensor | None = None
         self.k_norm: torch.Tensor | None = None
         self.position = build_part("position", self.param("position"), ctx)
@@ -564,7 +569,7 @@ class Attention(Part):
             group = self.n_heads // self.n_kv
             wide = group % 2 == 1 and plan.get("tiles_wide") is not None
             tiles = plan.get("tiles_wide") if wide else plan.get("tiles")
-            fast = (not self.softcap and tiles is not None and n_single < tokens and self._kernels(q.dtype)[1]
+            fast = (not self.softcap and self.sinks is None and tiles is not None and n_single < tokens and self._kernels(q.dtype)[1]
                     and ops.attention_prefill_tcgen05_measures_mass(group, cache.page_size, wide)
                     and ops.attention_prefill_tcgen05_supports(q, cache.k_pool, cache.page_size))
             n_simt = n_single if fast else tokens
@@ -572,15 +577,15 @@ class Attention(Part):
                 ops.attention_simt(q[:n_simt], cache.k_pool, cache.v_pool, table, batch.pos[:n_simt],
                                    batch.entry[:n_simt], out[:n_simt], cache.page_size, self.window, self.scale,
                                    batch.status, cache.mass_sum, cache.weight_sum, weights[:n_simt],
-                                   softcap=self.softcap)
+                                   softcap=self.softcap, sinks=self.sinks)
             if fast:
                 ops.attention_prefill_tcgen05(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size,
                                               self.window, self.scale, batch.status, 1, None, wide,
                                               mass=(weights, cache.mass_sum, cache.weight_sum))
             return
-        if self.softcap:
+        if self.softcap or self.sinks is not None:
             ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
-                               self.window, self.scale, batch.status, softcap=self.softcap)
+                               self.window, self.scale, batch.status, softcap=self.softcap, sinks=self.sinks)
             return
         plan = batch.plans.get(self.plan_key()) or {}
         decode_kernel, prefill_kernel = self._kernels(q.dtype)

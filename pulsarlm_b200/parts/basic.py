@@ -106,6 +106,86 @@ class RMSNorm(Part):
         return NormedDelta(y, self.weight_f32(), self.eps, mult, bias)
 
 
+@dataclasses.dataclass
+class LayerNormedDelta:
+    """A sublayer's output that enters the residual stream layer-normed:
+    x += (y - mean(y)) / sqrt(var(y) + eps) * weight + bias (weight and bias fp32). A block
+    hands it on in the place of a plain delta; the kernel that next reads the stream (the
+    cast for the next sublayer, or the model's last norm) norms and adds it in the same pass."""
+
+    y: torch.Tensor
+    weight: torch.Tensor
+    bias: torch.Tensor
+    eps: float
+
+
+def settle_pending(x: torch.Tensor, delta) -> None:
+    """Adds whatever is pending into the fp32 stream `x` now, for a reader that cannot fold the
+    add into its own kernel."""
+    if delta is None:
+        return
+    if isinstance(delta, LayerNormedDelta):
+        ops.add_layernorm(x, delta.y, delta.weight, delta.bias, delta.eps, None)
+    elif isinstance(delta, NormedDelta):
+        ops.add_normed_rmsnorm(x, delta.y, delta.weight, delta.mult, delta.eps, delta.weight, delta.eps, None, None,
+                               delta.bias)
+    elif isinstance(delta, torch.Tensor):
+        x.add_(delta)
+    else:
+        raise TypeError(f"a pending {type(delta).__name__} can only be added by the norm kernel made for it")
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Part):
+    """h = (v - mean(v)) / sqrt(var(v) + eps) * weight + bias over the fp32 residual stream,
+    var the mean of the squared deviations, with whatever is pending added first (v = x +
+    delta, x updated in place). `pending(y)` hands a sublayer's output on to be normed by this
+    norm on its way into the stream. params: hidden_size, eps. tensors: weight, bias
+    [hidden_size] (kept in float32)."""
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.eps = float(self.param("eps"))
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    @classmethod
+    def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
+        hidden = int(spec.params["hidden_size"])
+        return {spec.tensors["weight"]: TensorNeed((hidden,), role="vector"),
+                spec.tensors["bias"]: TensorNeed((hidden,), role="offset")}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.spec.tensors["weight"]].float().contiguous()
+        self.bias = tensors[self.spec.tensors["bias"]].float().contiguous()
+
+    def forward(self, x: torch.Tensor, delta=None, rows: torch.Tensor | None = None) -> torch.Tensor:
+        n = rows.numel() if rows is not None else x.shape[0]
+        out = torch.empty((n, self.hidden), dtype=self.ctx.dtype, device=x.device)
+        if isinstance(delta, LayerNormedDelta):
+            ops.add_layernorm(x, delta.y, delta.weight, delta.bias, delta.eps, out, self.weight, self.bias, self.eps,
+                              rows)
+        else:
+            settle_pending(x, delta)
+            ops.add_layernorm(x, None, None, None, 0.0, out, self.weight, self.bias, self.eps, rows)
+        return out
+
+    def pending(self, y: torch.Tensor) -> LayerNormedDelta:
+        return LayerNormedDelta(y, self.weight, self.bias, self.eps)
+
+    def stream(self, x: torch.Tensor, delta=None) -> torch.Tensor:
+        """The stream itself (not normed) in the engine's dtype, with whatever is pending added
+        first: the input of a sublayer that reads the stream as it is."""
+        out = torch.empty(x.shape, dtype=self.ctx.dtype, device=x.device)
+        if isinstance(delta, LayerNormedDelta):
+            ops.add_layernorm(x, delta.y, delta.weight, delta.bias, delta.eps, out)
+        else:
+            settle_pending(x, delta)
+            ops.add_layernorm(x, None, None, None, 0.0, out)
+        return out
+
+
 def rope_inverse_frequencies(theta: float, head_dim: int, rotary_dim: int, llama3: dict | None) -> list[float]:
     """Radians per position for each rotated pair, in Python floats (fp64).
 
@@ -124,27 +204,57 @@ def rope_inverse_frequencies(theta: float, head_dim: int, rotary_dim: int, llama
                 pass
             elif wavelength > original / low:
                 f = f / factor
-            else:
+            elif high != low:
                 smooth = (original / wavelength - low) / (high - low)
                 f = (1.0 - smooth) * f / factor + smooth * f
         out.append(f)
     return out
 
 
+def ramped_frequencies(theta: float, rotary_dim: int, ramp: dict) -> tuple[list[float], float]:
+    """Radians per position for each rotated pair when scaled and unscaled frequencies are
+    blended along a ramp over the pair index (the scaling known as YaRN), and the amplitude
+    that multiplies cos and sin. With f_i = theta^(-2i / d) and index(t) = d ln(original /
+    (2 pi t)) / (2 ln theta): lo = max(floor(index(fast)), 0), hi = min(ceil(index(slow)), d - 1),
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1); the frequency is r_i f_i / factor +
+    (1 - r_i) f_i and the amplitude 0.1 ln(factor) + 1. `ramp`: factor, original, fast, slow."""
+    factor, original = float(ramp["factor"]), float(ramp["original"])
+
+    def index(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(index(float(ramp["fast"]))), 0)
+    hi = min(math.ceil(index(float(ramp["slow"]))), rotary_dim - 1)
+    out = []
+    for pair in range(rotary_dim // 2):
+        f = theta ** (-2.0 * pair / rotary_dim)
+        r = min(max((pair - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f / factor * r + f * (1.0 - r))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
 @register_part("position", "rope")
 class Rope(Part):
     """Rotate-half rotary encoding. params: theta, head_dim, rotary_dim (even,
     <= head_dim; pairs are (j, j + rotary_dim / 2), dims past rotary_dim pass
-    through), llama3 (None or the four scaling numbers). No tensors."""
+    through), llama3 (None or the four scaling numbers), ramp (None or the four numbers of
+    `ramped_frequencies`, which also sets `amplitude`, the number cos and sin are multiplied
+    by; the frequencies' exponent is then 2j / rotary_dim). No tensors."""
 
     def __init__(self, spec: PartSpec, ctx: BuildContext):
         super().__init__(spec, ctx)
         self.head_dim = int(self.param("head_dim"))
         self.rotary_dim = int(self.param("rotary_dim"))
+        self.amplitude = 1.0
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
             raise ValueError(f"rope: rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
-        freqs = rope_inverse_frequencies(float(self.param("theta")), self.head_dim, self.rotary_dim,
-                                         spec.params.get("llama3"))
+        if spec.params.get("ramp"):
+            if spec.params.get("llama3"):
+                raise ValueError("rope: llama3 bands and a ramp exclude each other")
+            freqs, self.amplitude = ramped_frequencies(float(self.param("theta")), self.rotary_dim, spec.params["ramp"])
+        else:
+            freqs = rope_inverse_frequencies(float(self.param("theta")), self.head_dim, self.rotary_dim,
+                                             spec.params.get("llama3"))
         self.inv_freq = torch.tensor(freqs, dtype=torch.float64, device=ctx.device)
 
     def table(self) -> tuple[torch.Tensor | None, int]:
@@ -156,8 +266,10 @@ class RopePairs(Part):
     """Rotary encoding over neighbouring pairs: within the first `rotary_dim` columns of a
     vector, (2i, 2i + 1) turns by the angle pos * f_i with f_i = theta^(-2i / rotary_dim) /
     factor (`factor`: linear position scaling, 1 when absent); the other columns pass through.
-    params: theta, rotary_dim (even), factor (optional). No tensors. `table()` gives the fp64
-    radians per position and the rotary width; the mixer's kernel decides what a vector is."""
+    params: theta, rotary_dim (even), factor (optional), llama3 (optional: the four numbers of
+    the scaling by wavelength bands, see `rope_inverse_frequencies`). No tensors. `table()`
+    gives the fp64 radians per position and the rotary width; the mixer's kernel decides what
+    a vector is."""
 
     def __init__(self, spec: PartSpec, ctx: BuildContext):
         super().__init__(spec, ctx)
@@ -166,7 +278,8 @@ class RopePairs(Part):
             raise ValueError(f"rope_pairs: rotary_dim {self.rotary_dim} must be even and not negative")
         theta = float(self.param("theta"))
         factor = float(spec.params.get("factor") or 1.0)
-        freqs = [theta ** (-2.0 * i / self.rotary_dim) / factor for i in range(self.rotary_dim // 2)]
+        freqs = [f / factor for f in rope_inverse_frequencies(theta, max(self.rotary_dim, 1), self.rotary_dim,
+                                                              spec.params.get("llama3"))]
         self.inv_freq = torch.tensor(freqs, dtype=torch.float64, device=ctx.device)
 
     def table(self) -> tuple[torch.Tensor | None, int]:
@@ -254,17 +367,19 @@ class Head(Part):
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(Part):
     """(act(h Wg^T) * (h Wu^T)) Wd^T with act = SiLU
-    (pulsarlm-core/src/engine/model/llama.cpp:91). params: hidden_size,
-    intermediate_size, activation. tensors: gate, up [I, H], down [H, I].
+    (pulsarlm-core/src/engine/model/llama.cpp:91) or the tanh form of GELU. params:
+    hidden_size, intermediate_size, activation ("silu", the default, or "gelu_tanh").
+    tensors: gate, up [I, H], down [H, I].
     gate and up are stacked into one [2I, H] operand at load."""
 
     def __init__(self, spec: PartSpec, ctx: BuildContext):
         super().__init__(spec, ctx)
         self.hidden = int(self.param("hidden_size"))
         self.inter = int(self.param("intermediate_size"))
-        act = spec.params.get("activation", "silu")
-        if act != "silu":
-            raise ValueError(f"gated_mlp: unsupported activation {act!r} (supported: 'silu')")
+        self.activation = str(spec.params.get("activation") or "silu")
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated_mlp: unsupported activation {self.activation!r} (supported: 'silu', "
+                             f"'gelu_tanh')")
         self.gate_up: torch.Tensor | None = None
         self.down: torch.Tensor | None = None
 
@@ -280,7 +395,7 @@ class GatedMLP(Part):
         self.down = tensors[t["down"]].contiguous()
 
     def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
-        return gated_feed_forward(h, self.gate_up, self.down)
+        return gated_feed_forward(h, self.gate_up, self.down, self.activation)
 
 
 @register_part("feed_forward", "mlp")

@@ -11,7 +11,7 @@ import torch
 
 from . import native_layer
 from ..kernels import ops
-from .basic import NormedDelta, RMSNorm, ScaledPair
+from .basic import NormedDelta, RMSNorm, ScaledPair, settle_pending
 from .registry import BuildContext, build_part, register_part
 from .spec import LayerSpec
 
@@ -132,6 +132,60 @@ class SandwichNormBlock:
         else:
             y = self.feed_forward.forward(h, batch)
         return x, self.ff_out_norm.pending(y, self.mult, bias)
+
+
+@register_part("block", "post_norm")
+class PostNormBlock:
+    """The sublayers read the residual stream itself; the norm sits on what they return:
+
+        x += norm_mixer(mixer(x))
+        x += norm_ff(feed_forward(x))
+
+    Norm names in the LayerSpec: "mixer" and "feed_forward"; a LayerSpec whose feed_forward
+    is None has the first line only. The norms must know `pending(y)` (a sublayer's output
+    that is normed on its way into the stream): the kernel that makes the next reader's
+    input (the stream rounded to the engine's dtype) norms and adds the pending output in
+    the same pass. In float32 the sublayers read the stream in place."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext):
+        self.spec = spec
+        self.ctx = ctx
+        self.mixer_norm = build_part("norm", spec.norms["mixer"], ctx)
+        self.mixer = build_part("mixer", spec.mixer, ctx)
+        self.feed_forward = self.ff_norm = None
+        if spec.feed_forward is not None:
+            self.ff_norm = build_part("norm", spec.norms["feed_forward"], ctx)
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, ctx)
+        for norm in (self.mixer_norm, self.ff_norm):
+            if norm is not None and not hasattr(norm, "pending"):
+                raise ValueError(f"post_norm: the norm {norm.spec.kind!r} cannot be applied to a pending output")
+
+    @classmethod
+    def part_specs(cls, spec: LayerSpec):
+        out = [("norm", spec.norms["mixer"]), ("mixer", spec.mixer)]
+        if spec.feed_forward is not None:
+            out += [("norm", spec.norms["feed_forward"]), ("feed_forward", spec.feed_forward)]
+        return out
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None]
+
+    def cache_holders(self):
+        """The mixer and whatever else it keeps per request (`state_holders()`)."""
+        return [self.mixer] + list(getattr(self.mixer, "state_holders", lambda: [])())
+
+    def _read(self, x: torch.Tensor, delta) -> torch.Tensor:
+        """A sublayer's input: the stream with whatever is pending added first."""
+        if self.ctx.dtype == torch.float32:
+            settle_pending(x, delta)
+            return x
+        return self.mixer_norm.stream(x, delta)
+
+    def forward(self, x: torch.Tensor, delta, batch):
+        delta = self.mixer_norm.pending(self.mixer.forward(self._read(x, delta), batch))
+        if self.feed_forward is None:
+            return x, delta
+        return x, self.ff_norm.pending(self.feed_forward.forward(self._read(x, delta), batch))
 
 
 @register_part("block", "parallel")

@@ -120,13 +120,18 @@ def gated_linear(x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
 GATED_IN = os.environ.get("PULSARLM_B200_GATED_IN", "1") != "0"  # (0: always the SwiGLU kernel, for comparison)
 
 
-def gated_feed_forward(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
-    """(silu(x Wg^T) * (x Wu^T)) Wd^T -> [T, H]. For a handful of tokens in bfloat16 the down
-    projection's skinny kernel forms the gated activation itself as it reads the gate/up
-    projection's output (one launch fewer, the [T, I] activation never written); else
-    `gated_linear` followed by `linear`."""
+def gated_feed_forward(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """(act(x Wg^T) * (x Wu^T)) Wd^T -> [T, H], act "silu" or "gelu_tanh". With silu, for a handful
+    of tokens in bfloat16 the down projection's skinny kernel forms the gated activation itself as it
+    reads the gate/up projection's output (one launch fewer, the [T, I] activation never written);
+    else `gated_linear` followed by `linear`. Another activation: the product, the gating kernel with
+    that activation (fp32 arithmetic, one rounding), the product."""
     tokens, k = x.shape
     inter = gate_up.shape[0] // 2
+    if act != "silu":
+        gated = torch.empty((tokens, inter), dtype=x.dtype, device=x.device)
+        ops.gated_act(linear(x, gate_up), gated, act)
+        return linear(gated, down)
     if (GATED_IN and x.dtype == torch.bfloat16 == gate_up.dtype == down.dtype
             and tokens <= ops.GEMM_GATED_IN_MAX_TOKENS and down.stride(1) == 1
             and own_kernel_for(tokens, down.shape[0], x.device, inter) == "skinny"

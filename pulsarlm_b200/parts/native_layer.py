@@ -88,6 +88,8 @@ def eligible(block) -> bool:
         return False
     if type(block.mixer) is not Attention or type(block.feed_forward) is not GatedMLP:
         return False
+    if block.feed_forward.activation != "silu":
+        return False
     if block.mixer_norm.eps != block.ff_norm.eps or block.mixer_norm.weight.dtype != block.ff_norm.weight.dtype:
         return False
     mixer, ff = block.mixer, block.feed_forward

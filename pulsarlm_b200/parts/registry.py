@@ -72,8 +72,8 @@ def _load_builtins() -> None:
     global _builtins_loaded
     if not _builtins_loaded:
         _builtins_loaded = True
-        from . import (attention, basic, block, delta_rule, diff_attention, gated_delta, latent_attention, moe,  # noqa: F401
-                       short_conv)
+        from . import (attention, basic, block, conv_attention, delta_rule, diff_attention, gated_delta,  # noqa: F401
+                       latent_attention, moe, short_conv)
 
 
 def part_class(kind: str, name: str) -> type:
