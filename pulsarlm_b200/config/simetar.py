@@ -136,8 +136,9 @@ class SimetarConfig:
                 window = read_field(mask, "size", int) if isinstance(mask, dict) else None
                 if window is not None:
                     require_positive(f"layers[{i}].mixer.mask.size", window)
-                taps = read_field(mixer, "conv", int, 1)
-                require_positive(f"layers[{i}].mixer.conv", taps)
+                taps = read_field(mixer, "conv", int, None)     # None: no convolution and no taps stored
+                if taps is not None:
+                    require_positive(f"layers[{i}].mixer.conv", taps)
                 softcap = read_field(mixer, "softcap", float, None)
                 if softcap is not None and softcap <= 0.0:
                     raise ConfigError(f"config.json: layers[{i}].mixer.softcap must be positive, got {softcap}")
@@ -189,7 +190,9 @@ class SimetarConfig:
             mixer: dict = {"heads": layer.heads, "dim": layer.dim, "vdim": layer.value_dim, "scale": layer.scale,
                            "rot": rot}
             if layer.type == "attention":
-                mixer.update(kv_heads=layer.kv_heads, conv=layer.taps)
+                mixer.update(kv_heads=layer.kv_heads)
+                if layer.taps is not None:
+                    mixer["conv"] = layer.taps
                 if layer.window is not None:
                     mixer["mask"] = {"size": layer.window}
                 if layer.softcap is not None:

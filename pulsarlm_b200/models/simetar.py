@@ -34,15 +34,15 @@ def describe_simetar(cfg: SimetarConfig) -> ModelSpec:
                          "high_freq_factor": layer.scaling.high,
                          "original_max_position_embeddings": layer.scaling.original}
             position = PartSpec("rope_pairs", {"theta": layer.rot_base, "rotary_dim": layer.rot_dims, "llama3": bands})
+            names = {"q": m + "q", "q_bias": m + "q.b", "k": m + "k", "k_bias": m + "k.b", "q_norm": m + "q.norm",
+                     "k_norm": m + "k.norm", "gate": m + "g", "o": m + "o"}
+            if layer.taps is not None:  # (a single tap is still stored: one factor per channel)
+                names.update(q_conv=m + "q.conv", k_conv=m + "k.conv")
             mixer = PartSpec(
                 "conv_attention",
                 {"hidden_size": width, "n_heads": layer.heads, "n_kv_heads": layer.kv_heads, "head_dim": layer.dim,
                  "scale": layer.scale, "window": layer.window, "softcap": layer.softcap, "sink_logit": 0.0,
-                 "taps": layer.taps,
-                 "norm_eps": cfg.norm_eps, "position": position},
-                {"q": m + "q", "q_bias": m + "q.b", "k": m + "k", "k_bias": m + "k.b", "q_conv": m + "q.conv",
-                 "k_conv": m + "k.conv", "q_norm": m + "q.norm", "k_norm": m + "k.norm", "gate": m + "g",
-                 "o": m + "o"})
+                 "taps": layer.taps or 1, "norm_eps": cfg.norm_eps, "position": position}, names)
         else:
             position = PartSpec("rope", {"theta": layer.rot_base, "head_dim": layer.rot_dims,
                                          "rotary_dim": layer.rot_dims, "ramp": scaling})

@@ -32,7 +32,8 @@ class ConvAttention(Attention):
     plans) applies unchanged; what lies between the projection and the cache is one kernel
     (csrc/conv_norm_rope.cu) that also moves the state slot on in steps of single tokens.
 
-    params: hidden_size, n_heads, n_kv_heads, head_dim, taps (1: no convolution), norm_eps (with
+    params: hidden_size, n_heads, n_kv_heads, head_dim, taps (1 without the conv tensors: no
+    convolution; 1 with them: one factor per channel), norm_eps (with
     the q_norm / k_norm tensors), scale, window, softcap, sink_logit, position. tensors: q [nh*hd,
     H], k [nkv*hd, H], o [H, nh*hd]; optional q_bias [nh*hd], k_bias [nkv*hd], q_conv [nh*hd,
     taps], k_conv [nkv*hd, taps], q_norm [nh*hd], k_norm [nkv*hd], gate [nh*hd, H]."""
@@ -61,7 +62,7 @@ class ConvAttention(Attention):
                 needs[t[name + "_bias"]] = TensorNeed((rows,), role="offset")
             if t.get(name + "_norm"):
                 needs[t[name + "_norm"]] = TensorNeed((rows,), role="vector")
-            if taps > 1:
+            if t.get(name + "_conv"):
                 needs[t[name + "_conv"]] = TensorNeed((rows, taps))
         if t.get("gate"):
             needs[t["gate"]] = TensorNeed((nh * hd, h))
@@ -78,13 +79,17 @@ class ConvAttention(Attention):
             names = (t.get("q_" + kind), t.get("k_" + kind))
             if not any(names):
                 return None
+            if kind == "conv" and not all(names):
+                raise ValueError("conv_attention: q_conv and k_conv come together")
             nh, nkv, hd = self.n_heads, self.n_kv, self.head_dim
             parts = [tensors[n].float() if n else torch.zeros(rows, device=self.ctx.device)
                      for n, rows in zip(names, (nh * hd, nkv * hd))]
             return torch.cat(parts, dim=0).contiguous()
 
         self.bias = both("bias")
-        self.conv = both("conv") if self.taps > 1 else None
+        self.conv = both("conv")
+        if self.conv is None and self.taps > 1:
+            raise ValueError("conv_attention: more than one tap needs the q_conv / k_conv tensors")
         self.q_norm = tensors[t["q_norm"]].float().contiguous() if t.get("q_norm") else None
         self.k_norm = tensors[t["k_norm"]].float().contiguous() if t.get("k_norm") else None
 
