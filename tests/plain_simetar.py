@@ -109,6 +109,18 @@ def visible(n: int, window: int | None) -> torch.Tensor:
     return (back >= 0) & (back < window if window else back >= 0)
 
 
+def capped_attention_with_sink(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, see: torch.Tensor, scale: float,
+                               cap: float | None) -> torch.Tensor:
+    """One head: q [N, D], k [M, D], v [M, V], see [N, M]. Scores q . k * scale, squashed to
+    cap * tanh(s / cap) when there is a cap; weights exp(s_j) / (1 + sum over the visible exp(s)):
+    the 1 is a key with score 0 and no value, so a row's weights add up to less than 1."""
+    scores = (q @ k.T) * scale
+    if cap:
+        scores = cap * torch.tanh(scores / cap)
+    weights = torch.exp(scores).masked_fill(~see, 0.0)
+    return (weights / (1.0 + weights.sum(-1, keepdim=True))) @ v
+
+
 def _round(x: torch.Tensor, rounding) -> torch.Tensor:
     return x if rounding is None else x.to(rounding).double()
 
@@ -132,15 +144,10 @@ def conv_attention(mixer: dict, w: dict, p: str, h: torch.Tensor, eps: float, ro
     q = _round(rotate_neighbours(q, positions, freqs), rounding)
     k = _round(rotate_neighbours(k, positions, freqs), rounding)
     see = visible(n, (mixer.get("mask") or {}).get("size"))
-    cap = mixer.get("softcap")
     out = torch.zeros(n, heads, dim, dtype=torch.float64)
     for head in range(heads):
         g = head // (heads // kv_heads)
-        scores = (q[:, head] @ k[:, g].T) * mixer["scale"]
-        if cap:
-            scores = cap * torch.tanh(scores / cap)
-        weights = torch.exp(scores).masked_fill(~see, 0.0)
-        out[:, head] = (weights / (1.0 + weights.sum(-1, keepdim=True))) @ v[:, g]
+        out[:, head] = capped_attention_with_sink(q[:, head], k[:, g], v[:, g], see, mixer["scale"], mixer.get("softcap"))
     mixed = _round(_round(out.reshape(n, heads * dim), rounding) * torch.sigmoid(gate), rounding)
     return mixed @ w[p + "o"].T
 

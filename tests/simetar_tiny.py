@@ -109,14 +109,17 @@ def tensor_shapes(cfg: dict) -> dict[str, tuple[int, ...]]:
     return shapes
 
 
-def random_weights(cfg: dict, seed: int, dtype: torch.dtype = torch.float32) -> dict:
-    """Matrices N(0, 1/sqrt(in)) (queries, keys and the latent's projections twice that, so that
-    attention is far from uniform), norm weights 1 + 0.2 N (the norms on sublayer outputs 0.5 of
+def random_weights(cfg: dict, seed: int, dtype: torch.dtype = torch.float32, sharp: float = 1.0) -> dict:
+    """`sharp` multiplies every score (through the query norm's weight, or the query projection
+    where there is no such norm): with 3 or 4 a softmax rests on a few keys anywhere in reach, so
+    that one key too many or too few moves the logits by far more than a rounding. Matrices N(0, 1/sqrt(in)) (queries, keys and
+    the latent's projections twice that, so that attention is far from uniform), norm weights 1 + 0.2 N (the norms on sublayer outputs 0.5 of
     that, so that the stream grows slowly), biases 0.3 N, convolution taps N(0, 0.6); rounded to
     `dtype`."""
     gen = torch.Generator().manual_seed(seed)
     out = {}
-    for name, shape in tensor_shapes(cfg).items():
+    shapes = tensor_shapes(cfg)
+    for name, shape in shapes.items():
         leaf = name.split(".", 1)[1] if name[0] == "l" and "." in name else name
         if leaf.endswith(".b"):
             t = 0.3 * torch.randn(shape, generator=gen)
@@ -131,6 +134,8 @@ def random_weights(cfg: dict, seed: int, dtype: torch.dtype = torch.float32) -> 
         else:
             gain = 2.0 if leaf in ("mix.q", "mix.k", "mix.dkv", "mix.uk") else 1.0
             t = torch.randn(shape, generator=gen) * (gain / shape[1] ** 0.5)
+        if leaf == "mix.q.norm" or (leaf == "mix.q" and name + ".norm" not in shapes):
+            t = t * sharp
         out[name] = t.to(dtype)
     return out
 
@@ -167,11 +172,11 @@ class TinySimetar:
     model folder, and the plain implementation's logits on demand."""
 
     def __init__(self, key: str, dtype: str, seed: int = 1, cfg: dict | None = None, weights: dict | None = None,
-                 page: int = 16):
+                 page: int = 16, sharp: float = 1.0):
         self.cfg, self.page = CONFIGS[key] if cfg is None else (cfg, page)
         self.dtype = dtype
         torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
-        self.weights = weights if weights is not None else random_weights(self.cfg, seed, torch_dtype)
+        self.weights = weights if weights is not None else random_weights(self.cfg, seed, torch_dtype, sharp)
         self.weights = {k: v.to(torch_dtype) for k, v in self.weights.items()}
         self.plain_weights = {k: v.double() for k, v in self.weights.items()}
         self._dir = tempfile.TemporaryDirectory()
