@@ -571,6 +571,36 @@ def bunosun_config(width: int, runs: int, vocab: int = 32000) -> dict:
             "embedding": {"scale": float(width) ** 0.5}, "layers": layers, "loop": loop}
 
 
+def simetar_config(width: int, layers: int, vocab: int = 32000) -> dict:
+    """A Simetar model at a real model's layer sizes: conv attention (heads of 64 in groups of
+    four whose values are their keys, four taps, window 1,024, scores capped at 50, all of a head
+    rotated in neighbouring pairs with frequency bands) alternating with latent attention (16 heads
+    of 64 + 32 over a latent of 96 and a shared rotated part of 32, values of 64, ramped
+    frequencies); every fourth layer reads the latent cache of the layer two before it. Gated
+    feed-forward of 8/3 x width, the Llama layer's."""
+    ff = (8 * width // 3 + 255) // 256 * 256
+    mlp = {"kind": "dense", "ff": ff}
+    heads = width // 64
+    conv = {"type": "attention", "mlp": mlp,
+            "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 64, "conv": 4, "scale": 0.125,
+                      "softcap": 50.0, "mask": {"size": 1024},
+                      "rot": {"base": 500000.0, "dims": 64,
+                              "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 96, "scale": 0.1,
+                        "rot": {"base": 10000.0, "dims": 32,
+                                "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            out.append(conv)
+        elif i % 4 == 3:
+            out.append({**latent, "mixer": {**latent["mixer"], "kv_from": i - 2}})
+        else:
+            out.append(latent)
+    return {"architecture": "Simetar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
 def llama_config_like(width: int, layers: int, vocab: int = 32000) -> dict:
     """The Llama decoder at the same width, depth and vocabulary: heads of 64 in groups of
     four, gated feed-forward of 8/3 x width (the parameters of a plain one of 4 x width)."""
@@ -815,6 +845,128 @@ def bunosun_kernels(width: int, pk: dict) -> dict:
     return out
 
 
+def simetar_kernels(width: int, pk: dict) -> dict:
+    """The Simetar design's kernels alone at one layer's sizes, each beside the like kernel of the
+    Llama layer: milliseconds, algorithmic bytes or FLOPs, fraction of the copy bandwidth."""
+    import torch
+
+    from pulsarlm_b200.kernels import ops
+
+    dev, bf = "cuda:0", torch.bfloat16
+    out: dict = {}
+
+    def note(name, ms, nbytes=None, flops=None):
+        out[name] = {"ms": ms}
+        if nbytes is not None:
+            out[name].update(bytes=nbytes, frac_of_hbm=nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"])
+        if flops is not None:
+            out[name].update(tflops=flops / (ms / 1e3) / 1e12, frac_of_bf16=flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"])
+
+    heads, kv, hd, page, taps = width // 64, max(1, width // 256), 64, 16, 4
+    ff = (8 * width // 3 + 255) // 256 * 256
+    for tokens, entries in ((2048, 1), (8, 8), (64, 64)):
+        tag = f"T{tokens}_E{entries}"
+        per = tokens // entries
+        entry = torch.arange(entries, dtype=torch.int32, device=dev).repeat_interleave(per)
+        slots = torch.arange(entries, dtype=torch.int32, device=dev)
+        pos = torch.arange(per, dtype=torch.int32, device=dev).repeat(entries)
+        n_pages = entries * (per // page + 1)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(entries, -1)
+        x = torch.randn((tokens, width), device=dev)
+        y = torch.randn((tokens, width), device=dev).to(bf)
+        h = torch.empty_like(y)
+        w32 = torch.ones(width, device=dev)
+        # a sublayer's output normed into the stream, and the next reader's input, in one pass
+        note(f"add_layernorm_{tag}", time_kernel(lambda: ops.add_layernorm(x, y, w32, w32, 1e-6, h)),
+             tokens * width * (4 + 4 + 2 + 2))
+        note(f"add_rmsnorm_{tag} (Llama)", time_kernel(lambda: ops.add_rmsnorm(x, y, w32, 1e-6, h)),
+             tokens * width * (4 + 4 + 2 + 2))
+        # projection -> bias, convolution, two whole-projection norms, rotation, cache write
+        c = (heads + kv) * hd
+        proj = torch.randn((tokens, c + heads * hd), device=dev).to(bf)
+        bias, cw = torch.randn(c, device=dev), torch.randn((c, taps), device=dev)
+        state = torch.zeros((entries + 1, taps - 1, c), dtype=bf, device=dev)
+        pools = torch.zeros((2, n_pages, kv, page, hd), dtype=bf, device=dev)
+        q_out = torch.empty((tokens, heads * hd), dtype=bf, device=dev)
+        inv = torch.rand(hd // 2, dtype=torch.float64, device=dev)
+        qn, kn = torch.ones(heads * hd, device=dev), torch.ones(kv * hd, device=dev)
+
+        def conv_write():
+            ops.conv_norm_rope_write(proj[:, :c], bias, cw, state, slots, per == 1, qn, kn, 1e-6, inv, hd, True, 1.0,
+                                     pos, entry, table, q_out, pools[0], pools[1], page, heads, kv, hd)
+            if per > 1:
+                ops.short_conv_state_strided(proj[:, :c], entry, slots, state)
+        note(f"conv_norm_rope_write_{tag}", time_kernel(conv_write),
+             tokens * (c * 2 + heads * hd * 2 + 2 * kv * hd * 2) + entries * (taps - 1) * c * 2 * (2 if per == 1 else 1))
+        mixed = torch.randn((tokens, (heads + 2 * kv) * hd), device=dev).to(bf)
+        q_end, k_end = heads * hd, (heads + kv) * hd
+        note(f"rope_kv_write_{tag} (Llama)",
+             time_kernel(lambda: ops.rope_kv_write(mixed[:, :q_end].view(tokens, heads, hd),
+                                                   mixed[:, q_end:k_end].view(tokens, kv, hd),
+                                                   mixed[:, k_end:].view(tokens, kv, hd), pos, entry, table, pools[0],
+                                                   pools[1], page, inv, hd, None)),
+             tokens * (heads * hd * 2 * 2 + kv * hd * 2 * 4))
+        # the latent layer: norm of the latent, rotation of the shared key part and of the queries' rotated part
+        lh, ld, rot, rank = 16, 64, 32, 96
+        lq = torch.randn((tokens, lh, ld + rot), device=dev).to(bf)
+        lq_out = torch.empty((tokens, lh, rank + rot), dtype=bf, device=dev)
+        z = torch.randn((tokens, rank + rot), device=dev).to(bf)
+        lpool = torch.zeros((n_pages, 1, page, rank + rot), dtype=bf, device=dev)
+        inv16 = torch.rand(rot // 2, dtype=torch.float64, device=dev)
+        note(f"latent_rope_write_{tag}",
+             time_kernel(lambda: ops.latent_rope_write(lq, lq_out, z, torch.ones(rank, device=dev), 1e-6, rank, rot, inv16,
+                                                       False, 1.2, pos, entry, table, lpool, page)),
+             tokens * (lh * rot * 2 * 2 + (rank + rot) * 2 * 2))
+        # the feed-forward's and the mixers' gates
+        gate_up = torch.randn((tokens, 2 * ff), device=dev).to(bf)
+        act = torch.empty((tokens, ff), dtype=bf, device=dev)
+        note(f"gated_act_gelu_tanh_{tag}", time_kernel(lambda: ops.gated_act(gate_up, act, "gelu_tanh")), tokens * ff * 6)
+        note(f"swiglu_{tag} (Llama)", time_kernel(lambda: ops.swiglu(gate_up, act)), tokens * ff * 6)
+        note(f"sigmoid_gate_{tag}", time_kernel(lambda: ops.sigmoid_gate(q_out, proj[:, c:])), tokens * heads * hd * 6)
+    # attention of 64 single tokens over the last 1,024 of 2,048 keys: the cap and the sink, values
+    # in a pool of their own, beside the Llama layer's kernel at the same shape
+    keys, batch, window = 2048, 64, 1024
+    n_pages = batch * keys // page
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, keys // page)
+    pos = torch.full((batch,), keys - 1, dtype=torch.int32, device=dev)
+    ent = torch.arange(batch, dtype=torch.int32, device=dev)
+    q = torch.randn((batch, heads, hd), device=dev).to(bf)
+    res = torch.empty_like(q)
+    kvp = torch.randn((2, n_pages, kv, page, hd), device=dev).to(bf)
+    sinks = torch.zeros(heads, device=dev)
+    capped = ops.attention_extras(q, sinks, None, True, 50.0)
+    read = batch * window * kv * hd * 2 * 2
+    for splits in (1, 2, 4):
+        scratch = torch.empty(ops.attention_decode_scratch_floats(batch, heads, hd, splits), device=dev)
+        note(f"attention_decode_cap_sink_b64_w1024_splits{splits}",
+             time_kernel(lambda: ops.attention_decode(q, kvp[0], kvp[1], table, pos, ent, res, page, window, 0.125, splits,
+                                                      scratch, extras=capped)), read)
+        note(f"attention_decode_b64_w1024_splits{splits} (Llama)",
+             time_kernel(lambda: ops.attention_decode(q, kvp[0], kvp[1], table, pos, ent, res, page, window, 0.125, splits,
+                                                      scratch)), read)
+    note("attention_simt_cap_sink_b64_w1024 (the kernel of shapes the tensor-core kernels do not take)",
+         time_kernel(lambda: ops.attention_simt(q, kvp[0], kvp[1], table, pos, ent, res, page, window, 0.125,
+                                                softcap=50.0, sinks=sinks)), read)
+    # a 2,048-token prompt through the tiled kernel, with and without the cap and the sink
+    tokens = 2048
+    n_pages = tokens // page
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, n_pages)
+    q = torch.randn((tokens, heads, hd), device=dev).to(bf)
+    res = torch.empty_like(q)
+    kvp = torch.randn((2, n_pages, kv, page, hd), device=dev).to(bf)
+    rows = ops.attention_prefill_tile_rows()
+    tiles = torch.tensor([(r, min(rows, tokens - r), r, 0) for r in range(0, tokens, rows)], dtype=torch.int32,
+                         device=dev)
+    flops = 4.0 * heads * hd * sum(min(p + 1, window) for p in range(tokens))
+    for name, ex in (("cap, sink, split weights", ops.attention_extras(q, sinks, None, True, 50.0)),
+                     ("sink, split weights", ops.attention_extras(q, sinks, None, True)),
+                     ("plain: Llama", None)):
+        ms = time_kernel(lambda: ops.attention_prefill(q, kvp[0], kvp[1], table, tiles, res, page, window, 0.125,
+                                                       extras=ex))
+        note(f"attention_prefill_T2048_w1024 ({name})", ms, None, flops)
+    return out
+
+
 def run_design(args) -> dict:
     """Prefill and decode throughput of the named design at a few sizes beside the Llama
     decoder at the same width, depth and vocabulary (random weights), and the design's own
@@ -831,7 +983,8 @@ def run_design(args) -> dict:
     prompt, batch, context = 2048, 8, 2048
     with ClockSampler() as clocks:
         for width, layers in ((1024, 6), (2048, 6), (4096, 3)):
-            mine = bunosun_config(width, layers) if args.design == "bunosun" else rerilorn_config(width, layers)
+            mine = {"bunosun": bunosun_config, "rerilorn": rerilorn_config, "simetar": simetar_config}[args.design](
+                width, layers)
             for name, cfg in ((args.design, mine), ("llama", llama_config_like(width, layers))):
                 vocab = cfg.get("vocab", cfg.get("vocab_size"))
                 n_pages = (batch * (context + 256) + 4 * prompt) // PAGE_SIZE
@@ -863,7 +1016,8 @@ def run_design(args) -> dict:
                 del engine
                 gc.collect()
                 torch.cuda.empty_cache()
-        kernels = bunosun_kernels(2048, pk) if args.design == "bunosun" else design_kernels(2048, pk)
+        kernels = {"bunosun": bunosun_kernels, "rerilorn": design_kernels, "simetar": simetar_kernels}[args.design](
+            2048, pk)
     summary = clocks.summary()
     return {"metric": f"prefill and decode tok/s of the {args.design.capitalize()} design beside the Llama decoder at "
                       f"equal sizes",
@@ -877,8 +1031,8 @@ def run_design(args) -> dict:
 
 def main() -> int:
     p = argparse.ArgumentParser()
-    p.add_argument("--design", default="llama", choices=["llama", "rerilorn", "bunosun"],
-                   help="llama: the headline workload (the default); rerilorn, bunosun: that design's prefill and "
+    p.add_argument("--design", default="llama", choices=["llama", "rerilorn", "bunosun", "simetar"],
+                   help="llama: the headline workload (the default); rerilorn, bunosun, simetar: that design's prefill and "
                         "decode throughput at a few sizes beside the Llama decoder at equal sizes, and its kernels alone")
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=128)
@@ -901,7 +1055,7 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     args.warmup = max(3, args.warmup)
-    if args.design in ("rerilorn", "bunosun"):
+    if args.design in ("rerilorn", "bunosun", "simetar"):
         args.steps = min(args.steps, 64)
         print(json.dumps(run_design(args)))
         return 0

@@ -92,6 +92,8 @@ struct DecodeParams {
     const __nv_bfloat16* gate;
     int64_t gate_row_stride;
     int split_weights;
+    float cap_log2;        // score cap * log2 e (0: none) and scale / cap
+    float scale_over_cap;
 };
 
 // In-cluster merge: outputs are counted in groups of four dims ("vecs"); rank r owns
@@ -333,7 +335,9 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             for (int e = 0; e < 4; ++e) {
                 const int key = key0 + 8 * j + 2 * tig + (e & 1);
                 const bool ok = key >= first && key < ctx;
-                s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                const float scaled = EXTRAS ? pl_exponent_of_score(s[j][e], p.scale_log2, p.cap_log2, p.scale_over_cap)
+                                            : s[j][e] * p.scale_log2;
+                s[j][e] = ok ? scaled : -INFINITY;
             }
             tile_lo = fmaxf(tile_lo, fmaxf(s[j][0], s[j][1]));
             tile_hi = fmaxf(tile_hi, fmaxf(s[j][2], s[j][3]));
@@ -1031,6 +1035,7 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
     p.gate = nullptr;
     p.gate_row_stride = 0;
     p.split_weights = 0;
+    p.cap_log2 = p.scale_over_cap = 0.0f;
     if (extras != nullptr) {
         PL_REQUIRE(items == nullptr && tile_max == nullptr,
                    "attention_decode: sinks, gates and split weights are not taken over a work list or with attention mass");
@@ -1038,6 +1043,10 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
         p.gate = static_cast<const __nv_bfloat16*>(extras->gate);
         p.gate_row_stride = extras->gate_row_stride;
         p.split_weights = extras->split_weights;
+        if (extras->softcap > 0.0f) {
+            p.cap_log2 = extras->softcap * 1.4426950408889634f;
+            p.scale_over_cap = scale / extras->softcap;
+        }
     }
     p.n_heads = n_heads;
     p.group = group;

@@ -47,6 +47,8 @@ struct PrefillParams {
     const __nv_bfloat16* gate;
     int64_t gate_row_stride;
     int split_weights;
+    float cap_log2;        // score cap * log2 e (0: none) and scale / cap
+    float scale_over_cap;
 };
 
 // EXTRAS: the build that takes sinks, gates, split weights and one pool for keys and values; the
@@ -176,6 +178,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
                 }
             }
             float tile_lo = -INFINITY, tile_hi = -INFINITY;
+            auto exponent_of = [&](float raw) {
+                return EXTRAS ? pl_exponent_of_score(raw, p.scale_log2, p.cap_log2, p.scale_over_cap) : raw * p.scale_log2;
+            };
             // Only tiles that cross the diagonal or the window's edge need the mask.
             const int warp_first = pos0 + warp * 16;
             const bool edge = key0 + kBN - 1 > warp_first || (p.window > 0 && key0 < warp_last - p.window + 1);
@@ -185,8 +190,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int key = key0 + 8 * n + 2 * tig + e;
-                        s[n][e] = (key <= pos_lo && key >= first_lo) ? s[n][e] * p.scale_log2 : -INFINITY;
-                        s[n][2 + e] = (key <= pos_hi && key >= first_hi) ? s[n][2 + e] * p.scale_log2 : -INFINITY;
+                        s[n][e] = (key <= pos_lo && key >= first_lo) ? exponent_of(s[n][e]) : -INFINITY;
+                        s[n][2 + e] = (key <= pos_hi && key >= first_hi) ? exponent_of(s[n][2 + e]) : -INFINITY;
                     }
                     tile_lo = fmaxf(tile_lo, fmaxf(s[n][0], s[n][1]));
                     tile_hi = fmaxf(tile_hi, fmaxf(s[n][2], s[n][3]));
@@ -196,7 +201,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
                 for (int n = 0; n < kBN / 8; ++n) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        s[n][e] *= p.scale_log2;
+                        s[n][e] = exponent_of(s[n][e]);
                     }
                     tile_lo = fmaxf(tile_lo, fmaxf(s[n][0], s[n][1]));
                     tile_hi = fmaxf(tile_hi, fmaxf(s[n][2], s[n][3]));
@@ -312,7 +317,8 @@ int launch_prefill_build(const PrefillParams& p, int n_tiles, int n_heads, cudaS
 
 template <int HD>
 int launch_prefill(const PrefillParams& p, int n_tiles, int n_heads, cudaStream_t stream) {
-    const bool extras = p.sinks != nullptr || p.gate != nullptr || p.split_weights || p.v_pool == p.k_pool;
+    const bool extras = p.sinks != nullptr || p.gate != nullptr || p.split_weights || p.v_pool == p.k_pool ||
+                        p.cap_log2 > 0.0f;
     return extras ? launch_prefill_build<HD, true>(p, n_tiles, n_heads, stream)
                   : launch_prefill_build<HD, false>(p, n_tiles, n_heads, stream);
 }
@@ -373,6 +379,11 @@ PL_API int pl_attention_prefill(const void* q, int64_t q_row_stride, const void*
     p.gate = extras != nullptr ? static_cast<const __nv_bfloat16*>(extras->gate) : nullptr;
     p.gate_row_stride = extras != nullptr ? extras->gate_row_stride : 0;
     p.split_weights = extras != nullptr ? extras->split_weights : 0;
+    p.cap_log2 = p.scale_over_cap = 0.0f;
+    if (extras != nullptr && extras->softcap > 0.0f) {
+        p.cap_log2 = extras->softcap * 1.4426950408889634f;
+        p.scale_over_cap = scale / extras->softcap;
+    }
     switch (head_dim) {
         case 32: return launch_prefill<32>(p, n_tiles, n_heads, stream);
         case 48: return launch_prefill<48>(p, n_tiles, n_heads, stream);

@@ -157,13 +157,21 @@ __device__ __forceinline__ float pl_block_max(float v, float* scratch) {
 // gate_row_stride elements between rows; head h's output for token t is multiplied by
 // sigmoid(gate[t, h]). split_weights != 0: the tensor-core kernels feed the softmax weights
 // to the value product as two bfloat16 terms (the rounded weight and what the rounding
-// lost), so the weights keep 16 mantissa bits instead of 8.
+// lost), so the weights keep 16 mantissa bits instead of 8. softcap > 0: every scaled score s
+// becomes softcap * tanh(s / softcap) before the softmax.
 struct PlAttentionExtras {
     const float* sinks;
     const void* gate;
     int64_t gate_row_stride;
     int split_weights;
+    float softcap;
 };
+
+// A raw score on its way into the base-2 softmax: times scale * log2 e, or with a cap
+// cap * log2 e * tanh(raw * scale / cap). cap_log2 == 0: no cap.
+__device__ __forceinline__ float pl_exponent_of_score(float raw, float scale_log2, float cap_log2, float scale_over_cap) {
+    return cap_log2 > 0.0f ? cap_log2 * tanhf(raw * scale_over_cap) : raw * scale_log2;
+}
 
 // The factor that turns an accumulated row (sum of exp2(s - m) * v, with l the sum of
 // exp2(s - m)) into the head's output: 1 / l, or with a sink exp2(m - m') / (l exp2(m - m') +

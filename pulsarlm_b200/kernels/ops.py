@@ -996,24 +996,27 @@ def attention_decode_ctas_per_sm(head_dim: int) -> int:
 
 
 class _AttentionExtras(ctypes.Structure):
-    _fields_ = [("sinks", _PTR), ("gate", _PTR), ("gate_row_stride", _I64), ("split_weights", _I32)]
+    _fields_ = [("sinks", _PTR), ("gate", _PTR), ("gate_row_stride", _I64), ("split_weights", _I32),
+                ("softcap", _F32)]
 
 
 def attention_extras(q: torch.Tensor, sinks: torch.Tensor | None, gate: torch.Tensor | None,
-                     split_weights: bool) -> "_AttentionExtras | None":
+                     split_weights: bool, softcap: float = 0.0) -> "_AttentionExtras | None":
     """What the tensor-core attention kernels take beyond plain softmax attention (the struct
     PlAttentionExtras): sinks fp32 [nh] (exp(sinks[h]) joins head h's denominator), gate [T, nh]
     logits in q's dtype (outputs times their sigmoid), split_weights (softmax weights enter the
-    value product as two bfloat16 terms). None when nothing is asked for. The tensors must
-    outlive the call that takes the struct."""
-    if sinks is None and gate is None and not split_weights:
+    value product as two bfloat16 terms), softcap (> 0: scaled scores pass through softcap *
+    tanh(s / softcap)). None when nothing is asked for. The tensors must outlive the call that
+    takes the struct."""
+    if sinks is None and gate is None and not split_weights and not softcap:
         return None
     _dev(sinks, gate)
     if sinks is not None:
         assert sinks.dtype == torch.float32 and sinks.shape == (q.shape[1],) and sinks.is_contiguous()
     if gate is not None:
         assert gate.dtype == q.dtype and gate.shape == (q.shape[0], q.shape[1]) and gate.stride(1) == 1
-    return _AttentionExtras(_p(sinks), _p(gate), gate.stride(0) if gate is not None else 0, int(bool(split_weights)))
+    return _AttentionExtras(_p(sinks), _p(gate), gate.stride(0) if gate is not None else 0, int(bool(split_weights)),
+                            float(softcap or 0.0))
 
 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,

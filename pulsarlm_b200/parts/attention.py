@@ -421,9 +421,6 @@ class Attention(Part):
         if self.cache is None or self.ctx.dtype != torch.bfloat16:
             return None
         decode_kernel, prefill_kernel = self._kernels(self.ctx.dtype)
-        if self.softcap:
-            return (f"attention with a score cap ({self.softcap:g}) runs on the CUDA-core attention kernel, the "
-                    f"only one that squashes scores; expect it several times slower than uncapped attention")
         if decode_kernel and prefill_kernel:
             return None
         return (f"attention with head size {self.head_dim}, {self.n_heads // self.n_kv} query heads per kv head and "
@@ -434,9 +431,15 @@ class Attention(Part):
     def measures_mass_in_captured_steps(self) -> bool:
         """Whether this layer can measure attention mass inside a captured decode step
         (the tensor-core decode kernel takes its shape and it has no score cap)."""
-        if self.cache is None or self.softcap:
+        if self.cache is None or self._wants_extras():
             return False
         return self._kernels(self.ctx.dtype)[0]
+
+    def _wants_extras(self) -> bool:
+        """A score cap or a sink term: the tensor-core kernels take them in their build with
+        extras (csrc/attention_decode.cu, attention_prefill.cu), without work lists, wide tiles
+        or attention mass."""
+        return bool(self.softcap) or self.sinks is not None
 
     def plan_key(self):
         """Layers of equal tiling share one plan: the tile lists depend on the kernels'
@@ -445,7 +448,7 @@ class Attention(Part):
             return None
         wide = (self.n_heads // self.n_kv) % 2 == 1
         return ("attention", self.cache.page_size, self.head_dim, self.n_heads // self.n_kv, wide,
-                self.ctx.dtype, bool(self.softcap), self.n_kv, self.window)
+                self.ctx.dtype, self._wants_extras(), self.n_kv, self.window)
 
     def native_key(self):
         """What `native_choice` depends on beyond `plan_key`: layers that agree in both get
@@ -460,7 +463,7 @@ class Attention(Part):
         only; such replays get a capture of their own, whose decode attention walks a work
         list (see plan_step). Else None."""
         decode_kernel, _ = self._kernels(self.ctx.dtype)
-        if not decode_kernel or self.softcap or not DECODE_ITEMS or not step.n_decode:
+        if not decode_kernel or self._wants_extras() or not DECODE_ITEMS or not step.n_decode:
             return None
         if self.cache.mass_sum is not None and self.cache_from is None:
             return None
@@ -484,11 +487,11 @@ class Attention(Part):
         is captured and replayed: the most it may come to read)."""
         decode_kernel, prefill_kernel = self._kernels(self.ctx.dtype)
         plan: dict = {"tiles": None, "tiles_wide": None, "max_keys": 0, "max_context": 0}
-        if self.softcap:
-            return plan  # every token goes to the CUDA-core kernel, which needs no plan
+        extras = self._wants_extras()
         n_decode = step.n_decode if decode_kernel else 0
         if n_decode:
             plan["max_context"] = step.context_bound if step.fixed_shape else max(step.context_lens[:n_decode])
+        if n_decode and not extras:  # (a score cap or a sink: equal shares, no work list)
             # Many single tokens (so many that their keys would not be split at all): a work
             # list cut by the requests' true lengths instead of one CTA per request and kv
             # head, unless attention mass is measured (that path keeps equal shares).
@@ -521,7 +524,7 @@ class Attention(Part):
             start = step.context_lens[e] - n
             for r in range(0, n, rows):
                 tiles.append((at + r, min(rows, n - r), start + r, e))
-            if wide_rows > rows:
+            if wide_rows > rows and not extras:
                 for r in range(0, n, wide_rows):
                     wide_tiles.append((at + r, min(wide_rows, n - r), start + r, e))
         tiles.sort(key=lambda t: -(t[2] + t[1]))
@@ -531,6 +534,43 @@ class Attention(Part):
             wide_tiles.sort(key=lambda t: -(t[2] + t[1]))
             plan["tiles_wide"] = np.array(wide_tiles, dtype=np.int32).reshape(len(wide_tiles), 4)
         return plan
+
+    def _attend_with_extras(self, q, out, table, batch, plan, decode_kernel: bool, prefill_kernel: bool) -> None:
+        """Attention with a score cap and / or a sink term. bfloat16 shapes the tensor-core
+        kernels take: the leading single tokens on the split-key kernel, prompt portions on
+        the tiled mma.sync kernel, both in their build with extras (the cap on every score
+        in fp32, the sink in the row's last step, softmax weights in two bfloat16 terms);
+        everything else on the CUDA-core kernel."""
+        cache = self.cache
+        tokens = q.shape[0]
+        n_decode = min(int(batch.n_decode), tokens) if decode_kernel else 0
+        if n_decode > 0:
+            max_context = plan.get("max_context") or max(batch.host_context_lens[:n_decode])
+            if self.window:
+                max_context = min(max_context, self.window + 16)
+            splits = decode_splits(n_decode * self.n_kv, max_context, q.device, self.head_dim,
+                                   self.n_heads // self.n_kv)
+            scratch = None
+            if splits > 1:
+                scratch = torch.empty(ops.attention_decode_scratch_floats(n_decode, self.n_heads, self.head_dim,
+                                                                          splits),
+                                      dtype=torch.float32, device=q.device)
+            ops.attention_decode(q[:n_decode], cache.k_pool, cache.v_pool, table, batch.pos[:n_decode],
+                                 batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window, self.scale,
+                                 splits, scratch, batch.status,
+                                 extras=ops.attention_extras(q[:n_decode], self.sinks, None, True, self.softcap))
+        if n_decode == tokens:
+            return
+        tiles = plan.get("tiles")
+        if prefill_kernel and tiles is not None and n_decode == int(batch.n_decode):
+            # (the tile list covers exactly the tokens after the leading single tokens)
+            ops.attention_prefill(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size, self.window,
+                                  self.scale, batch.status,
+                                  extras=ops.attention_extras(q, self.sinks, None, True, self.softcap))
+            return
+        ops.attention_simt(q[n_decode:], cache.k_pool, cache.v_pool, table, batch.pos[n_decode:],
+                           batch.entry[n_decode:], out[n_decode:], cache.page_size, self.window, self.scale,
+                           batch.status, softcap=self.softcap, sinks=self.sinks)
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch, rope: tuple | None = None) -> None:
         """out = attention of q over the cache. The batch's leading `n_decode` tokens
@@ -583,12 +623,11 @@ class Attention(Part):
                                               self.window, self.scale, batch.status, 1, None, wide,
                                               mass=(weights, cache.mass_sum, cache.weight_sum))
             return
-        if self.softcap or self.sinks is not None:
-            ops.attention_simt(q, cache.k_pool, cache.v_pool, table, batch.pos, batch.entry, out, cache.page_size,
-                               self.window, self.scale, batch.status, softcap=self.softcap, sinks=self.sinks)
-            return
         plan = batch.plans.get(self.plan_key()) or {}
         decode_kernel, prefill_kernel = self._kernels(q.dtype)
+        if self._wants_extras():
+            self._attend_with_extras(q, out, table, batch, plan, decode_kernel, prefill_kernel)
+            return
         n_decode = min(int(batch.n_decode), tokens) if decode_kernel else 0
         if n_decode > 0 and plan.get("decode_items") is not None:
             items = plan["decode_items"]

@@ -247,6 +247,72 @@ def test_capped_attention_with_a_sink_at_window_edges(window, spike, cap):
         assert plain.relative_error(out.cpu(), want) < (1e-5 if dtype == torch.float32 else 1e-2), (dtype, window, spike)
 
 
+@pytest.mark.parametrize("dim,heads,kv", [(32, 6, 2), (96, 4, 1), (64, 3, 3)])
+@pytest.mark.parametrize("window,distance", [(None, None), (None, 150), (24, 23), (24, 24), (37, 36), (37, 37), (16, 15)])
+@pytest.mark.parametrize("cap", [None, 3.0, 50.0])
+def test_tensor_core_attention_takes_the_cap_and_the_sink(dim, heads, kv, window, distance, cap):
+    """The bfloat16 kernels for single tokens (any number of key shares) and for prompt portions,
+    with values apart from the keys, a score cap and a sink of logit 0; one key at a chosen
+    distance (a window's last key, the first one outside, or far back) is lined up with the query."""
+    ops = _ops()
+    page, scale, dtype = 16, 0.25, torch.bfloat16
+    lengths = [200, 33, 16, 129]
+    if not (ops.attention_decode_supports(dim, heads // kv, page, dtype) and ops.attention_prefill_supports(dim, page, dtype)):
+        pytest.skip("a shape for the CUDA-core kernel")
+    sinks = torch.zeros(heads, device=DEV)
+
+    def case(queries, seed):
+        gen = torch.Generator().manual_seed(seed)
+        n_pages, table = _paged(lengths, page, gen)
+        keys = [torch.randn(n, kv, dim, generator=gen).to(dtype) for n in lengths]
+        values = [torch.randn(n, kv, dim, generator=gen).to(dtype) for n in lengths]
+        q = torch.randn(len(queries), heads, dim, generator=gen).to(dtype)
+        if distance is not None:
+            for i, (e, p) in enumerate(queries):
+                if p - distance >= 0:
+                    direction = q[i, 0].float() / q[i, 0].float().norm()
+                    keys[e][p - distance, 0] = (60.0 * direction).to(dtype)
+        k_pool = torch.zeros(n_pages, kv, page, dim, dtype=dtype, device=DEV)
+        v_pool = torch.zeros_like(k_pool)
+        for e, n in enumerate(lengths):
+            for j in range(n):
+                k_pool[table[e, j // page], :, j % page] = keys[e][j].to(DEV)
+                v_pool[table[e, j // page], :, j % page] = values[e][j].to(DEV)
+        want = torch.zeros(len(queries), heads, dim, dtype=torch.float64)
+        for i, (e, p) in enumerate(queries):
+            see = plain.visible(lengths[e], window)[p: p + 1]
+            for h in range(heads):
+                g = h // (heads // kv)
+                want[i, h] = plain.capped_attention_with_sink(q[i, h].double()[None], keys[e][:, g].double(),
+                                                              values[e][:, g].double(), see, scale, cap)[0]
+        return q.to(DEV), k_pool, v_pool, table.to(DEV), want
+
+    queries = [(e, n - 1) for e, n in enumerate(lengths)] + [(0, 0), (0, 1), (3, 64)]
+    # (a request has one single token in a step; here each query row stands for a request of its own)
+    q, k_pool, v_pool, table, want = case(queries, 21)
+    pos, entry = _i32([p for _, p in queries]), _i32([e for e, _ in queries])
+    for splits in (1, 2, 5):
+        scratch = torch.empty(ops.attention_decode_scratch_floats(len(queries), heads, dim, splits),
+                              dtype=torch.float32, device=DEV) if splits > 1 else None
+        out = torch.empty_like(q)
+        ops.attention_decode(q, k_pool, v_pool, table, pos, entry, out, page, window, scale, splits, scratch,
+                             extras=ops.attention_extras(q, sinks, None, True, cap or 0.0))
+        assert plain.relative_error(out.cpu(), want) < 1e-2, ("single tokens", splits)
+    spans = [(0, 120, 200), (3, 0, 129), (1, 32, 33), (2, 0, 16)]
+    queries = [(e, p) for e, lo, hi in spans for p in range(lo, hi)]
+    q, k_pool, v_pool, table, want = case(queries, 22)
+    rows = ops.attention_prefill_tile_rows()
+    tiles, at = [], 0
+    for e, lo, hi in spans:
+        for r in range(0, hi - lo, rows):
+            tiles.append((at + r, min(rows, hi - lo - r), lo + r, e))
+        at += hi - lo
+    out = torch.empty_like(q)
+    ops.attention_prefill(q, k_pool, v_pool, table, _i32(tiles), out, page, window, scale,
+                          extras=ops.attention_extras(q, sinks, None, True, cap or 0.0))
+    assert plain.relative_error(out.cpu(), want) < 1e-2, "prompt rows"
+
+
 # --------------------------------------------------------------------------- whole models
 
 def _model(key, dtype, seed=1, sharp=1.0):
