@@ -894,10 +894,12 @@ def simetar_kernels(width: int, pk: dict) -> dict:
         def conv_write():
             ops.conv_norm_rope_write(proj[:, :c], bias, cw, state, slots, per == 1, qn, kn, 1e-6, inv, hd, True, 1.0,
                                      pos, entry, table, q_out, pools[0], pools[1], page, heads, kv, hd)
-            if per > 1:
-                ops.short_conv_state_strided(proj[:, :c], entry, slots, state)
         note(f"conv_norm_rope_write_{tag}", time_kernel(conv_write),
              tokens * (c * 2 + heads * hd * 2 + 2 * kv * hd * 2) + entries * (taps - 1) * c * 2 * (2 if per == 1 else 1))
+        if per > 1:  # (steps of single tokens move the stored inputs on in the launch above)
+            note(f"short_conv_state_strided_{tag} (the portions' last inputs, kept for the next step)",
+                 time_kernel(lambda: ops.short_conv_state_strided(proj[:, :c], entry, slots, state)),
+                 entries * (taps - 1) * c * 2 * 2)
         mixed = torch.randn((tokens, (heads + 2 * kv) * hd), device=dev).to(bf)
         q_end, k_end = heads * hd, (heads + kv) * hd
         note(f"rope_kv_write_{tag} (Llama)",

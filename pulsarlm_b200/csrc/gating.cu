@@ -67,6 +67,26 @@ __global__ void sigmoid_gate_kernel(scalar_t* __restrict__ x, int64_t x_stride, 
     }
 }
 
+// Four channels a thread, for widths, strides and addresses that are multiples of four elements.
+template <typename scalar_t>
+__global__ void sigmoid_gate_quads_kernel(scalar_t* __restrict__ x, int64_t x_stride, const scalar_t* __restrict__ gate,
+                                          int64_t gate_stride, int64_t tokens, int width) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    const int quads = width / 4;
+    const int64_t total = tokens * quads;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t t = idx / quads;
+        const int i = 4 * static_cast<int>(idx - t * quads);
+        scalar_t* at = x + t * x_stride + i;
+        const float4 v = pl_load4(at);
+        const float4 g = pl_load4(gate + t * gate_stride + i);
+        pl_store4(at, make_float4(v.x / (1.0f + expf(-g.x)), v.y / (1.0f + expf(-g.y)), v.z / (1.0f + expf(-g.z)),
+                                  v.w / (1.0f + expf(-g.w))));
+    }
+}
+
 }  // namespace
 
 // in [T, 2 * width] (gate columns, then up columns), out [T, width], both dense, in the
@@ -104,9 +124,19 @@ PL_API int pl_sigmoid_gate(void* x, int64_t x_stride, const void* gate, int64_t 
         return 0;
     }
     const int threads = 256;
-    const int64_t total = static_cast<int64_t>(n_tokens) * width;
+    const uintptr_t piece = dtype == PL_F32 ? 16 : 8;  // four elements
+    const bool quads = width % 4 == 0 && x_stride % 4 == 0 && gate_stride % 4 == 0 &&
+        reinterpret_cast<uintptr_t>(x) % piece == 0 && reinterpret_cast<uintptr_t>(gate) % piece == 0;
+    const int64_t total = static_cast<int64_t>(n_tokens) * (quads ? width / 4 : width);
     const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
     PL_DISPATCH_DTYPE(dtype, "sigmoid_gate", {
+        if (quads) {
+            pl_launch_overlapped(sigmoid_gate_quads_kernel<scalar_t>, dim3(blocks), dim3(threads), 0, stream,
+                                 static_cast<scalar_t*>(x), x_stride, static_cast<const scalar_t*>(gate), gate_stride,
+                                 n_tokens, width);
+            PL_CHECK_LAUNCH("sigmoid_gate");
+            return 0;
+        }
         pl_launch_overlapped(sigmoid_gate_kernel<scalar_t>, dim3(blocks), dim3(threads), 0, stream,
                              static_cast<scalar_t*>(x), x_stride, static_cast<const scalar_t*>(gate), gate_stride,
                              n_tokens, width);

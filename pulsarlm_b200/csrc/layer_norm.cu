@@ -10,6 +10,9 @@
 // block per row, the row kept in shared memory. Statistics and the residual sum are fp32
 // and added in an order that depends on the width alone, so a row's result does not depend
 // on what else is in the batch.
+#include <algorithm>
+#include <cstdint>
+
 #include "common.cuh"
 
 namespace {
@@ -82,6 +85,119 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const scalar_t* __re
     }
 }
 
+// The same for widths that are a multiple of four and at most 4 * PER * blockDim: a thread keeps
+// its PER groups of four channels in registers from the first load to the last store, and every
+// load that does not wait for a statistic (the stream's row, the weights) is issued before the
+// first reduction.
+template <typename scalar_t, int PER>
+__global__ void add_layernorm_vec_kernel(float* __restrict__ x, const scalar_t* __restrict__ y,
+                                         const float* __restrict__ wy, const float* __restrict__ by, float eps_y,
+                                         scalar_t* __restrict__ out, const float* __restrict__ w,
+                                         const float* __restrict__ b, float eps, const int32_t* __restrict__ rows,
+                                         int hidden, int norm_out) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int64_t s = rows != nullptr ? rows[r] : r;
+    float* xr = x + s * hidden;
+    const float n = static_cast<float>(hidden);
+    float4 v[PER];
+    bool mine[PER];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+        mine[k] = i < hidden;
+        v[k] = mine[k] ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    auto sum_of = [&](const float4 (&q)[PER]) {
+        float local = 0.0f;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            local += (q[k].x + q[k].y) + (q[k].z + q[k].w);  // (groups that are not this thread's hold zeros)
+        }
+        return pl_block_sum(local, scratch);
+    };
+    auto squares_of = [&](const float4 (&q)[PER], float mean) {
+        float local = 0.0f;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            if (mine[k]) {
+                const float dx = q[k].x - mean, dy = q[k].y - mean, dz = q[k].z - mean, dw = q[k].w - mean;
+                local += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+            }
+        }
+        return pl_block_sum(local, scratch);
+    };
+    if (y != nullptr) {
+        const scalar_t* yr = y + s * hidden;
+        float4 u[PER], g[PER], o[PER];
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = (threadIdx.x + k * blockDim.x) * 4;
+            const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            u[k] = mine[k] ? pl_load4(yr + i) : zero;
+            g[k] = mine[k] ? *reinterpret_cast<const float4*>(wy + i) : zero;
+            o[k] = mine[k] ? *reinterpret_cast<const float4*>(by + i) : zero;
+        }
+        const float mean = sum_of(u) / n;
+        const float inv = 1.0f / sqrtf(squares_of(u, mean) / n + eps_y);
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            if (mine[k]) {
+                v[k].x = v[k].x + ((u[k].x - mean) * inv * g[k].x + o[k].x);
+                v[k].y = v[k].y + ((u[k].y - mean) * inv * g[k].y + o[k].y);
+                v[k].z = v[k].z + ((u[k].z - mean) * inv * g[k].z + o[k].z);
+                v[k].w = v[k].w + ((u[k].w - mean) * inv * g[k].w + o[k].w);
+                if (rows == nullptr) {
+                    *reinterpret_cast<float4*>(xr + (threadIdx.x + k * blockDim.x) * 4) = v[k];
+                }
+            }
+        }
+    }
+    if (out == nullptr) {
+        return;
+    }
+    scalar_t* outr = out + static_cast<int64_t>(r) * hidden;
+    if (!norm_out) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            if (mine[k]) {
+                pl_store4(outr + (threadIdx.x + k * blockDim.x) * 4, v[k]);
+            }
+        }
+        return;
+    }
+    float4 g[PER], o[PER];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+        const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        g[k] = mine[k] ? *reinterpret_cast<const float4*>(w + i) : zero;
+        o[k] = mine[k] ? *reinterpret_cast<const float4*>(b + i) : zero;
+    }
+    const float mean = sum_of(v) / n;
+    const float inv = 1.0f / sqrtf(squares_of(v, mean) / n + eps);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        if (mine[k]) {
+            pl_store4(outr + (threadIdx.x + k * blockDim.x) * 4,
+                      make_float4((v[k].x - mean) * inv * g[k].x + o[k].x, (v[k].y - mean) * inv * g[k].y + o[k].y,
+                                  (v[k].z - mean) * inv * g[k].z + o[k].z, (v[k].w - mean) * inv * g[k].w + o[k].w));
+        }
+    }
+}
+
+template <typename scalar_t, int PER>
+void launch_add_layernorm_vec(float* x, const void* y, const float* wy, const float* by, float eps_y, void* out,
+                              const float* w, const float* b, float eps, const int32_t* rows, int n_rows, int hidden,
+                              int norm_out, cudaStream_t stream) {
+    const int threads = std::max(32, ((hidden / 4 + PER - 1) / PER + 31) / 32 * 32);
+    pl_launch_overlapped(add_layernorm_vec_kernel<scalar_t, PER>, dim3(n_rows), dim3(threads), 0, stream, x,
+                         static_cast<const scalar_t*>(y), wy, by, eps_y, static_cast<scalar_t*>(out), w, b, eps, rows,
+                         hidden, norm_out);
+}
+
 }  // namespace
 
 // x fp32 [T, hidden] (updated in place unless `rows` is given); y [T, hidden] in the engine's
@@ -104,7 +220,24 @@ PL_API int pl_add_layernorm(float* x, const void* y, const float* wy, const floa
     }
     const int threads = hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128;
     const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+    auto whole = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+    const bool groups = hidden % 4 == 0 && hidden <= 8192 && whole(x) && whole(y) && whole(wy) && whole(by) &&
+                        whole(out) && whole(w) && whole(b);
     PL_DISPATCH_DTYPE(dtype, "add_layernorm", {
+        if (groups) {
+            if (hidden <= 2048) {
+                launch_add_layernorm_vec<scalar_t, 1>(x, y, wy, by, eps_y, out, w, b, eps, rows, n_rows, hidden, norm_out,
+                                                      stream);
+            } else if (hidden <= 4096) {
+                launch_add_layernorm_vec<scalar_t, 2>(x, y, wy, by, eps_y, out, w, b, eps, rows, n_rows, hidden, norm_out,
+                                                      stream);
+            } else {
+                launch_add_layernorm_vec<scalar_t, 4>(x, y, wy, by, eps_y, out, w, b, eps, rows, n_rows, hidden, norm_out,
+                                                      stream);
+            }
+            PL_CHECK_LAUNCH("add_layernorm");
+            return 0;
+        }
         if (smem > 48 * 1024) {
             cudaFuncSetAttribute(add_layernorm_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem));

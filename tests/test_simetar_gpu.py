@@ -34,7 +34,7 @@ def _bar(dtype) -> float:
 
 # --------------------------------------------------------------------------- mechanisms alone
 
-@pytest.mark.parametrize("width", [24, 100, 520])
+@pytest.mark.parametrize("width", [24, 50, 100, 520, 2600, 6000, 8200])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_layer_norm_of_a_sublayers_output_joins_the_stream(width, dtype):
     """x += layernorm(y) * w + b in fp32; the reader's copy is the stream rounded, or (the model's
@@ -82,6 +82,13 @@ def test_tanh_gelu_gate_and_sigmoid_gate(dtype):
     ops.sigmoid_gate(xd, wide[:, 140:])
     want = x.double() * torch.sigmoid(wide[:, 140:].cpu().double())
     assert plain.relative_error(xd.cpu(), want) < _bar(dtype)
+    # columns that start off a four-element border, and a width that is no multiple of four
+    for first, width in ((137, 60), (140, 57)):
+        x = torch.randn(7, width, generator=gen).to(dtype)
+        xd = x.to(DEV)
+        ops.sigmoid_gate(xd, wide[:, first: first + width])
+        want = x.double() * torch.sigmoid(wide[:, first: first + width].cpu().double())
+        assert plain.relative_error(xd.cpu(), want) < _bar(dtype)
 
 
 def _paged(lengths, page, gen):
@@ -95,9 +102,11 @@ def _paged(lengths, page, gen):
     return n_pages, table
 
 
-@pytest.mark.parametrize("taps,heads,kv,dim,rotary", [(3, 4, 2, 16, 16), (1, 3, 3, 8, 4), (4, 6, 2, 12, 0), (2, 2, 1, 32, 24)])
+@pytest.mark.parametrize("taps,heads,kv,dim,rotary", [(3, 4, 2, 16, 16), (1, 3, 3, 8, 4), (4, 6, 2, 12, 0), (2, 2, 1, 32, 24),
+                                                      (5, 2, 1, 16, 8), (4, 36, 4, 128, 64), (3, 5, 1, 10, 6)])
+@pytest.mark.parametrize("pairs", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_convolution_norm_and_rotation_on_the_way_to_the_cache(taps, heads, kv, dim, rotary, dtype):
+def test_convolution_norm_and_rotation_on_the_way_to_the_cache(taps, heads, kv, dim, rotary, pairs, dtype):
     """Two requests; the first step brings portions of 5 and 1 tokens (so the second request's
     filter starts in the middle of a batch), the second a portion and a single token that reach
     back into the stored inputs, the third single tokens of both (the launch that also moves the
@@ -128,7 +137,11 @@ def test_convolution_norm_and_rotation_on_the_way_to_the_cache(taps, heads, kv, 
         q = (plain.rms(yq, eps) * q_norm.double()).view(n, heads, dim)
         k = (plain.rms(yk, eps) * k_norm.double()).view(n, kv, dim)
         if rotary:
-            q, k = plain.rotate_neighbours(q, positions, freqs), plain.rotate_neighbours(k, positions, freqs)
+            def turn(x):
+                if pairs:
+                    return plain.rotate_neighbours(x, positions, freqs)
+                return torch.cat([plain.rotate_halves(x[..., :rotary], positions, freqs, 1.0), x[..., rotary:]], dim=-1)
+            q, k = turn(q), turn(k)
         want_q.append(q.reshape(n, heads * dim))
         want_k.append(k)
         want_v.append(yk.view(n, kv, dim))
@@ -141,7 +154,7 @@ def test_convolution_norm_and_rotation_on_the_way_to_the_cache(taps, heads, kv, 
         entry = _i32([e for e, n in portions for _ in range(n)])
         q_out = torch.empty(rows.shape[0], heads * dim, dtype=dtype, device=DEV)
         ops.conv_norm_rope_write(rows[:, :channels], bias.to(DEV), conv.to(DEV), states, slots, single,
-                                 q_norm.to(DEV), k_norm.to(DEV), eps, freqs.to(DEV) if rotary else None, rotary, True,
+                                 q_norm.to(DEV), k_norm.to(DEV), eps, freqs.to(DEV) if rotary else None, rotary, pairs,
                                  1.0, pos, entry, table.to(DEV), q_out, k_pool, v_pool, page, heads, kv, dim)
         if taps > 1 and not single:
             ops.short_conv_state_strided(rows[:, :channels], entry, slots, states)
@@ -158,6 +171,40 @@ def test_convolution_norm_and_rotation_on_the_way_to_the_cache(taps, heads, kv, 
         got_v = torch.stack([v_pool[pages[j // page], :, j % page].float().cpu() for j in range(n)])
         assert plain.relative_error(got_k, want_k[e][:n]) < _bar(dtype), "cached keys"
         assert plain.relative_error(got_v, want_v[e][:n]) < _bar(dtype), "cached values"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_convolution_kernel_gives_the_same_bits_in_a_long_step_and_in_short_ones(dtype):
+    """A long portion runs on smaller blocks than a short one; queries, keys, values and the
+    stored inputs come out the same bits whether 400 tokens arrive at once or in pieces."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(3)
+    taps, heads, kv, dim, page, n = 4, 6, 2, 32, 16, 400
+    channels = (heads + kv) * dim
+    proj = (torch.randn(n, channels, generator=gen) * 2).to(dtype).to(DEV)
+    bias, conv = torch.randn(channels, generator=gen).to(DEV), torch.randn(channels, taps, generator=gen).to(DEV)
+    q_norm, k_norm = (torch.rand(heads * dim, generator=gen) + 0.5).to(DEV), (torch.rand(kv * dim, generator=gen) + 0.5).to(DEV)
+    freqs = plain.banded_frequencies({"base": 100.0, "dims": dim, "scaling": None}).to(DEV)
+    n_pages, table = _paged([n], page, gen)
+    results = []
+    for cuts in ([n], [100, 1, 1, 198, 100]):
+        k_pool = torch.zeros(n_pages, kv, page, dim, dtype=dtype, device=DEV)
+        v_pool = torch.zeros_like(k_pool)
+        states = torch.zeros(2, taps - 1, channels, dtype=dtype, device=DEV)
+        q_out = torch.empty(n, heads * dim, dtype=dtype, device=DEV)
+        at = 0
+        for m in cuts:
+            rows = proj[at: at + m]
+            entry = _i32([0] * m)
+            ops.conv_norm_rope_write(rows, bias, conv, states, _i32([1]), m == 1, q_norm, k_norm, 1e-6, freqs, dim, True, 1.0,
+                                     _i32(list(range(at, at + m))), entry, table.to(DEV), q_out[at: at + m], k_pool, v_pool,
+                                     page, heads, kv, dim)
+            if m > 1:
+                ops.short_conv_state_strided(rows, entry, _i32([1]), states)
+            at += m
+        results.append((q_out, k_pool, v_pool, states))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("heads,dim,rot,rank", [(3, 16, 8, 40), (2, 8, 4, 24), (4, 32, 16, 48), (1, 16, 32, 20)])
