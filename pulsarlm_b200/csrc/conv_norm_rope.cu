@@ -150,12 +150,12 @@ __device__ __forceinline__ void row_unpack(const uint4& raw, float (&o)[4]) {
     o[3] = __uint_as_float(raw.w);
 }
 __device__ __forceinline__ void row_unpack(const uint4& raw, float (&o)[8]) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    // (a bfloat16 is the upper half of a float: shifts and masks, no conversion unit)
+    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(h[i]);
-        o[2 * i] = f.x;
-        o[2 * i + 1] = f.y;
+        o[2 * i] = __uint_as_float(words[i] << 16);
+        o[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
     }
 }
 __device__ __forceinline__ uint4 row_pack(const float (&v)[4]) {
@@ -286,8 +286,8 @@ __global__ void conv_norm_rope_vec_kernel(
         }
         piece_squares[ch / N] = squares;
     }
-    // Both sums in an order that the sizes alone decide (not the block's size, which follows the
-    // number of tokens): the first warp adds the pieces' sums, lane l those of pieces l, l + 32, ...
+    // Both sums in an order that the sizes alone decide (not the block's size): the first warp adds
+    // the pieces' sums, lane l those of pieces l, l + 32, ...
     __syncthreads();
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x, q_pieces = q_width / N, pieces = width / N;
@@ -476,9 +476,7 @@ bool launch_conv_pieces(const void* proj, int64_t row_stride, const float* bias,
     if (!pieces) {
         return false;
     }
-    // Few tokens: a thread per piece, so that a token's loads are all in flight at once. Many: small
-    // blocks, of which an SM holds more, so that one block's loads hide another's reductions.
-    const int threads = n_tokens > 2 * 148 ? 128 : std::min(512, std::max(32, (width / kN + 31) / 32 * 32));
+    const int threads = std::min(512, std::max(32, (width / kN + 31) / 32 * 32));  // a thread per piece, up to 512
     smem += static_cast<size_t>(width / kN) * sizeof(float);
     if (smem > 200 * 1024) {
         return false;

@@ -175,8 +175,8 @@ def test_convolution_norm_and_rotation_on_the_way_to_the_cache(taps, heads, kv, 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_convolution_kernel_gives_the_same_bits_in_a_long_step_and_in_short_ones(dtype):
-    """A long portion runs on smaller blocks than a short one; queries, keys, values and the
-    stored inputs come out the same bits whether 400 tokens arrive at once or in pieces."""
+    """Queries, keys, values and the stored inputs come out the same bits whether 400 tokens
+    arrive at once or in pieces, single tokens among them."""
     ops = _ops()
     gen = torch.Generator().manual_seed(3)
     taps, heads, kv, dim, page, n = 4, 6, 2, 32, 16, 400
