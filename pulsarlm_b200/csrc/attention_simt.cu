@@ -14,7 +14,8 @@
 
 namespace {
 
-constexpr int kMaxAcc = 16;  // head_dim <= 512
+constexpr int kMaxAcc = 16;      // head_dim <= 512
+constexpr int kMaxAccWide = 32;  // head_dim <= 1024
 
 template <typename scalar_t>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const scalar_t* __restrict__ k, int head_dim);
@@ -64,7 +65,7 @@ __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict_
     return s;
 }
 
-template <typename scalar_t>
+template <typename scalar_t, int ACC>
 __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_row_stride,
                                       const scalar_t* __restrict__ k_pool, const scalar_t* __restrict__ v_pool,
                                       int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
@@ -95,9 +96,9 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
         __syncwarp();
 
         float m = -INFINITY, l = 0.0f;
-        float acc[kMaxAcc];
+        float acc[ACC];
 #pragma unroll
-        for (int i = 0; i < kMaxAcc; ++i) {
+        for (int i = 0; i < ACC; ++i) {
             acc[i] = 0.0f;
         }
         // Attention mass (optional): per page and head, this query's weight times its
@@ -158,7 +159,7 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
             const float pw = offset >= 0 && seen ? expf(s - m_new) : 0.0f;
             l = l * corr + pl_warp_sum(pw);
 #pragma unroll
-            for (int i = 0; i < kMaxAcc; ++i) {
+            for (int i = 0; i < ACC; ++i) {
                 if (i < n_acc) {
                     acc[i] *= corr;
                 }
@@ -172,7 +173,7 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
                 }
                 const scalar_t* vrow = v_pool + oj;
 #pragma unroll
-                for (int i = 0; i < kMaxAcc; ++i) {
+                for (int i = 0; i < ACC; ++i) {
                     const int d = lane + 32 * i;
                     if (i < n_acc && d < head_dim) {
                         acc[i] = fmaf(pj, pl_load(vrow + d), acc[i]);
@@ -192,7 +193,7 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
             const float corr = m > -INFINITY ? expf(m - m_new) : 0.0f;
             l = l * corr + expf(sink - m_new);
 #pragma unroll
-            for (int i = 0; i < kMaxAcc; ++i) {
+            for (int i = 0; i < ACC; ++i) {
                 if (i < n_acc) {
                     acc[i] *= corr;
                 }
@@ -205,7 +206,7 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
         }
         scalar_t* orow = out + t * out_row_stride + static_cast<int64_t>(h) * head_dim;
 #pragma unroll
-        for (int i = 0; i < kMaxAcc; ++i) {
+        for (int i = 0; i < ACC; ++i) {
             const int d = lane + 32 * i;
             if (i < n_acc && d < head_dim) {
                 pl_store(orow + d, acc[i] * inv);
@@ -240,8 +241,8 @@ PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_
                n_kv_heads, head_dim, page_size);
     PL_REQUIRE(n_heads % n_kv_heads == 0, "attention: %d query heads are not a multiple of %d kv heads", n_heads,
                n_kv_heads);
-    PL_REQUIRE(head_dim <= 32 * kMaxAcc, "attention: head_dim %d exceeds the supported maximum %d", head_dim,
-               32 * kMaxAcc);
+    PL_REQUIRE(head_dim <= 32 * kMaxAccWide, "attention: head_dim %d exceeds the supported maximum %d", head_dim,
+               32 * kMaxAccWide);
     PL_REQUIRE(n_kv_heads <= 65535, "attention: %d kv heads exceed the grid limit", n_kv_heads);
     PL_REQUIRE(mass_sum == nullptr || weight_sum != nullptr, "attention: attention mass needs weight_sum too");
     if (n_tokens == 0) {
@@ -252,7 +253,10 @@ PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_
     const size_t smem = static_cast<size_t>(warps) * head_dim * sizeof(float);
     const dim3 grid(n_tokens, n_kv_heads);
     PL_DISPATCH_DTYPE(dtype, "attention", {
-        attention_simt_kernel<scalar_t><<<grid, warps * 32, smem, stream>>>(
+        // (rows above 512 take the build with twice the accumulators a lane)
+        auto kernel = head_dim <= 32 * kMaxAcc ? attention_simt_kernel<scalar_t, kMaxAcc>
+                                               : attention_simt_kernel<scalar_t, kMaxAccWide>;
+        kernel<<<grid, warps * 32, smem, stream>>>(
             static_cast<const scalar_t*>(q), q_row_stride, static_cast<const scalar_t*>(k_pool),
             static_cast<const scalar_t*>(v_pool), page_stride, head_stride, page_size, n_pages, table, table_width,
             pos, entry, static_cast<scalar_t*>(out), out_row_stride, n_heads, group, head_dim, window, scale,

@@ -610,6 +610,23 @@ def test_sizes_come_from_the_configuration():
         tm.check(tokens, harness.replay(tm.runner(8), steps), "sizes of one")
 
 
+def test_latent_rows_wider_than_512():
+    """A latent of 560 with a rotated part of 32: cached rows of 592 attend on the CUDA-core kernel's
+    build with more accumulators a lane."""
+    cfg = {
+        "architecture": "Simetar", "vocab": 60, "width": 48, "norm": {"eps": 1e-5},
+        "layers": [st.latent_layer(2, 16, 32, 8, 560, st.dense(64), scale=0.2, ramp=(4.0, 32, 16.0, 1.0)),
+                   st.attention_layer(2, 1, 16, 9, 8, 3, None, softcap=8.0),
+                   st.latent_layer(3, 8, 32, 24, 560, None, scale=0.2, ramp=(4.0, 32, 16.0, 1.0), kv_from=0)],
+    }
+    for dtype in ("float32", "bfloat16"):
+        tm = st.TinySimetar("-", dtype, cfg=cfg)
+        tokens = {"p": st.random_tokens(cfg, 45, 51)}
+        steps = [([("p", tokens["p"][:30], list(range(30)))], [])]
+        steps += [([("p", [t], [0])], []) for t in tokens["p"][30:]]
+        tm.check(tokens, harness.replay(tm.runner(8), steps), "rows of 592")
+
+
 def _random_config(seed: int) -> dict:
     """Sizes, constants and layer order drawn at random: widths that are no multiple of 8, odd
     head counts, head sizes and ranks with and without a tensor-core kernel, windows from 1 up,
