@@ -94,6 +94,8 @@ struct DecodeParams {
     int split_weights;
     float cap_log2;        // score cap * log2 e (0: none) and scale / cap
     float scale_over_cap;
+    const float* distance_bias;  // fp32 [bias_rows, n_heads] (nullptr: none), see PlAttentionExtras
+    int bias_rows;
 };
 
 // In-cluster merge: outputs are counted in groups of four dims ("vecs"); rank r owns
@@ -335,8 +337,15 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
             for (int e = 0; e < 4; ++e) {
                 const int key = key0 + 8 * j + 2 * tig + (e & 1);
                 const bool ok = key >= first && key < ctx;
-                const float scaled = EXTRAS ? pl_exponent_of_score(s[j][e], p.scale_log2, p.cap_log2, p.scale_over_cap)
-                                            : s[j][e] * p.scale_log2;
+                float scaled = EXTRAS ? pl_exponent_of_score(s[j][e], p.scale_log2, p.cap_log2, p.scale_over_cap)
+                                      : s[j][e] * p.scale_log2;
+                if (EXTRAS && p.distance_bias != nullptr && ok) {
+                    // the bias of this head (row g, or g + 8, of the group) at the key's distance, in the exponent's units
+                    const int hg = min(e < 2 ? g : g + 8, p.group - 1);
+                    const int d = min(ctx - 1 - key, p.bias_rows - 1);
+                    scaled = fmaf(__ldg(p.distance_bias + static_cast<int64_t>(d) * p.n_heads + kv_head * p.group + hg),
+                                  1.4426950408889634f, scaled);
+                }
                 s[j][e] = ok ? scaled : -INFINITY;
             }
             tile_lo = fmaxf(tile_lo, fmaxf(s[j][0], s[j][1]));
@@ -1036,7 +1045,12 @@ int run_attention_decode(bool allow_cluster, const void* q, int64_t q_row_stride
     p.gate_row_stride = 0;
     p.split_weights = 0;
     p.cap_log2 = p.scale_over_cap = 0.0f;
+    p.distance_bias = nullptr;
+    p.bias_rows = 0;
     if (extras != nullptr) {
+        p.distance_bias = extras->distance_bias;
+        p.bias_rows = extras->bias_rows;
+        PL_REQUIRE(p.distance_bias == nullptr || p.bias_rows > 0, "attention_decode: a distance bias needs rows");
         PL_REQUIRE(items == nullptr && tile_max == nullptr,
                    "attention_decode: sinks, gates and split weights are not taken over a work list or with attention mass");
         p.sinks = extras->sinks;

@@ -49,9 +49,12 @@ struct PrefillParams {
     int split_weights;
     float cap_log2;        // score cap * log2 e (0: none) and scale / cap
     float scale_over_cap;
+    const float* distance_bias;  // fp32 [bias_rows, n_heads] (nullptr: none), see PlAttentionExtras
+    int bias_rows;
+    int n_heads;
 };
 
-// EXTRAS: the build that takes sinks, gates, split weights and one pool for keys and values; the
+// EXTRAS: the build that takes sinks, gates, split weights, a bias by distance and one pool for keys and values; the
 // plain build is compiled without any of it.
 template <int HD, bool EXTRAS>
 __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const PrefillParams p) {
@@ -178,8 +181,17 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
                 }
             }
             float tile_lo = -INFINITY, tile_hi = -INFINITY;
-            auto exponent_of = [&](float raw) {
-                return EXTRAS ? pl_exponent_of_score(raw, p.scale_log2, p.cap_log2, p.scale_over_cap) : raw * p.scale_log2;
+            // (with a bias by distance: the table's entry for this head, in the exponent's units)
+            auto exponent_of = [&](float raw, int key, int pos) {
+                if (!EXTRAS) {
+                    return raw * p.scale_log2;
+                }
+                float x = pl_exponent_of_score(raw, p.scale_log2, p.cap_log2, p.scale_over_cap);
+                if (p.distance_bias != nullptr) {
+                    const int d = min(max(pos - key, 0), p.bias_rows - 1);
+                    x = fmaf(__ldg(p.distance_bias + static_cast<int64_t>(d) * p.n_heads + head), 1.4426950408889634f, x);
+                }
+                return x;
             };
             // Only tiles that cross the diagonal or the window's edge need the mask.
             const int warp_first = pos0 + warp * 16;
@@ -190,8 +202,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int key = key0 + 8 * n + 2 * tig + e;
-                        s[n][e] = (key <= pos_lo && key >= first_lo) ? exponent_of(s[n][e]) : -INFINITY;
-                        s[n][2 + e] = (key <= pos_hi && key >= first_hi) ? exponent_of(s[n][2 + e]) : -INFINITY;
+                        s[n][e] = (key <= pos_lo && key >= first_lo) ? exponent_of(s[n][e], key, pos_lo) : -INFINITY;
+                        s[n][2 + e] = (key <= pos_hi && key >= first_hi) ? exponent_of(s[n][2 + e], key, pos_hi) : -INFINITY;
                     }
                     tile_lo = fmaxf(tile_lo, fmaxf(s[n][0], s[n][1]));
                     tile_hi = fmaxf(tile_hi, fmaxf(s[n][2], s[n][3]));
@@ -201,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
                 for (int n = 0; n < kBN / 8; ++n) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        s[n][e] = exponent_of(s[n][e]);
+                        s[n][e] = exponent_of(s[n][e], key0 + 8 * n + 2 * tig + (e & 1), e < 2 ? pos_lo : pos_hi);
                     }
                     tile_lo = fmaxf(tile_lo, fmaxf(s[n][0], s[n][1]));
                     tile_hi = fmaxf(tile_hi, fmaxf(s[n][2], s[n][3]));
@@ -318,7 +330,7 @@ int launch_prefill_build(const PrefillParams& p, int n_tiles, int n_heads, cudaS
 template <int HD>
 int launch_prefill(const PrefillParams& p, int n_tiles, int n_heads, cudaStream_t stream) {
     const bool extras = p.sinks != nullptr || p.gate != nullptr || p.split_weights || p.v_pool == p.k_pool ||
-                        p.cap_log2 > 0.0f;
+                        p.cap_log2 > 0.0f || p.distance_bias != nullptr;
     return extras ? launch_prefill_build<HD, true>(p, n_tiles, n_heads, stream)
                   : launch_prefill_build<HD, false>(p, n_tiles, n_heads, stream);
 }
@@ -379,6 +391,10 @@ PL_API int pl_attention_prefill(const void* q, int64_t q_row_stride, const void*
     p.gate = extras != nullptr ? static_cast<const __nv_bfloat16*>(extras->gate) : nullptr;
     p.gate_row_stride = extras != nullptr ? extras->gate_row_stride : 0;
     p.split_weights = extras != nullptr ? extras->split_weights : 0;
+    p.distance_bias = extras != nullptr ? extras->distance_bias : nullptr;
+    p.bias_rows = extras != nullptr ? extras->bias_rows : 0;
+    p.n_heads = n_heads;
+    PL_REQUIRE(p.distance_bias == nullptr || p.bias_rows > 0, "attention_prefill: a distance bias needs rows");
     p.cap_log2 = p.scale_over_cap = 0.0f;
     if (extras != nullptr && extras->softcap > 0.0f) {
         p.cap_log2 = extras->softcap * 1.4426950408889634f;

@@ -75,7 +75,8 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
                                       int head_dim, int window, float scale, float softcap,
                                       float* __restrict__ mass_sum, float* __restrict__ weight_sum,
                                       const float* __restrict__ query_weights, const float* __restrict__ sinks,
-                                      const scalar_t* __restrict__ gate, int64_t gate_row_stride, int32_t* status) {
+                                      const scalar_t* __restrict__ gate, int64_t gate_row_stride,
+                                      const float* __restrict__ distance_bias, int bias_rows, int32_t* status) {
     extern __shared__ float q_shared[];  // [warps][head_dim]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -132,6 +133,10 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
                     s = dot_row<scalar_t>(qs, k_pool + offset, head_dim) * scale;
                     if (softcap > 0.0f) {
                         s = softcap * tanhf(s / softcap);  // scores squashed into (-cap, cap) before the softmax
+                    }
+                    if (distance_bias != nullptr) {
+                        // a learned bias by distance and head joins the scaled score (the scale does not touch it)
+                        s += distance_bias[static_cast<int64_t>(min(p - j, bias_rows - 1)) * n_heads + h];
                     }
                 } else if (status != nullptr) {
                     atomicOr(status, 4);
@@ -228,14 +233,17 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
 // score s becomes softcap * tanh(s / softcap) before the softmax (0: off). sinks (fp32
 // [n_heads], may be nullptr): exp(sinks[h]) is added to head h's softmax denominator. gate
 // ([T, n_heads] logits with gate_row_stride elements between rows, may be nullptr): head
-// h's output for token t is multiplied by sigmoid(gate[t, h]).
+// h's output for token t is multiplied by sigmoid(gate[t, h]). distance_bias (fp32 [bias_rows,
+// n_heads], may be nullptr): distance_bias[min(pos - key's position, bias_rows - 1), h] is added
+// to head h's scaled score.
 PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
                              int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
                              const int32_t* table, int table_width, const int32_t* pos, const int32_t* entry,
                              void* out, int64_t out_row_stride, int n_tokens, int n_heads, int n_kv_heads,
                              int head_dim, int window, float scale, float softcap, int dtype, float* mass_sum,
                              float* weight_sum, const float* query_weights, const float* sinks, const void* gate,
-                             int64_t gate_row_stride, int32_t* status, cudaStream_t stream) {
+                             int64_t gate_row_stride, const float* distance_bias, int bias_rows, int32_t* status,
+                             cudaStream_t stream) {
     PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && page_size > 0,
                "attention: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d page=%d", n_tokens, n_heads,
                n_kv_heads, head_dim, page_size);
@@ -245,6 +253,7 @@ PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_
                32 * kMaxAccWide);
     PL_REQUIRE(n_kv_heads <= 65535, "attention: %d kv heads exceed the grid limit", n_kv_heads);
     PL_REQUIRE(mass_sum == nullptr || weight_sum != nullptr, "attention: attention mass needs weight_sum too");
+    PL_REQUIRE(distance_bias == nullptr || bias_rows > 0, "attention: a distance bias needs rows");
     if (n_tokens == 0) {
         return 0;
     }
@@ -261,7 +270,7 @@ PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_
             static_cast<const scalar_t*>(v_pool), page_stride, head_stride, page_size, n_pages, table, table_width,
             pos, entry, static_cast<scalar_t*>(out), out_row_stride, n_heads, group, head_dim, window, scale,
             softcap, mass_sum, weight_sum, query_weights, sinks, static_cast<const scalar_t*>(gate), gate_row_stride,
-            status);
+            distance_bias, bias_rows, status);
     });
     PL_CHECK_LAUNCH("attention");
     return 0;

@@ -1,15 +1,17 @@
 // A routed feed-forward (mixture of experts): the router, and the experts' products for
 // steps of few tokens and for the float32 engine.
 //
-// Router (pl_moe_route), all fp32: logits z = W_r h, scores s = softmax(z) over all experts,
-// choice scores c = s + correction. Experts form `n_groups` equal groups of neighbours; a
-// group's score is its largest choice score, and only experts of the `keep` best groups can
-// be chosen (the others count as minus infinity). The `top` largest choice scores are
-// chosen (ties go to the lower index); their weights are their scores s (without the
-// correction) over the chosen scores' sum (+ 1e-20). One block per token.
+// Router (pl_moe_route), all fp32: logits z = W_r h, scores s = softmax(z) over all experts
+// (or, `sigmoid_scores`, s = sigmoid(z) of each alone), choice scores c = s + correction.
+// Experts form `n_groups` equal groups of neighbours; a group's score is the sum of its
+// `group_top` largest choice scores (1: its largest), and only experts of the `keep` best
+// groups can be chosen (the others count as minus infinity). The `top` largest choice scores
+// are chosen (ties go to the lower index); their weights are their scores s (without the
+// correction), with `renormalise` over the chosen scores' sum (+ 1e-20). One block per token.
 //
 // Experts (pl_moe_gate_up, pl_moe_down): expert e of a token computes W_down,e (silu(W_gate,e h)
-// * (W_up,e h)). The first kernel takes a (token, chosen expert) pair per block row and writes
+// * (W_up,e h)); pl_moe_up takes the place of pl_moe_gate_up for experts without a gate, W_down,e
+// act(W_up,e h) with act the square of relu. The first kernel takes a (token, chosen expert) pair per block row and writes
 // the gated activation, a warp per feature (both rows of the feature read with 16-byte loads,
 // the lanes' shares added in a fixed order); the second takes a token per block row and adds
 // up its experts' down projections times their weights, plus an optional row that every
@@ -24,6 +26,8 @@
 #include "common.cuh"
 
 namespace {
+
+constexpr int kMaxGroupTop = 8;  // a group's score adds up at most this many of its experts' scores
 
 __device__ __forceinline__ float silu_f32(float z) { return z / (1.0f + expf(-z)); }
 
@@ -71,7 +75,7 @@ template <typename scalar_t, int TOKENS>
 __global__ void __launch_bounds__(512, TOKENS > 1 ? 2 : 1) moe_route_kernel(const scalar_t* __restrict__ h, int64_t h_stride, const float* __restrict__ router,
                                  const float* __restrict__ correction, int32_t* __restrict__ ids,
                                  float* __restrict__ weights, int n_tokens, int hidden, int n_experts, int top,
-                                 int n_groups, int keep) {
+                                 int n_groups, int keep, int sigmoid_scores, int group_top, int renormalise) {
     pl_grid_trigger();
     pl_grid_wait();
     extern __shared__ float shared[];
@@ -168,32 +172,56 @@ __global__ void __launch_bounds__(512, TOKENS > 1 ? 2 : 1) moe_route_kernel(cons
     float* score = scores + warp * n_experts;
     float* choice = choices + warp * n_experts;
     float* group_score = group_scores + warp * n_groups;
-    float top_z = -INFINITY;
-    for (int e = lane; e < n_experts; e += 32) {
-        top_z = fmaxf(top_z, score[e]);
-    }
-    top_z = pl_warp_max(top_z);
-    float sum = 0.0f;
-    for (int e = lane; e < n_experts; e += 32) {
-        const float x = expf(score[e] - top_z);
-        score[e] = x;
-        sum += x;
-    }
-    sum = pl_warp_sum(sum);
-    for (int e = lane; e < n_experts; e += 32) {
-        const float s = score[e] / sum;
-        score[e] = s;
-        choice[e] = s + (correction != nullptr ? correction[e] : 0.0f);
+    if (sigmoid_scores) {
+        for (int e = lane; e < n_experts; e += 32) {
+            const float s = 1.0f / (1.0f + expf(-score[e]));
+            score[e] = s;
+            choice[e] = s + (correction != nullptr ? correction[e] : 0.0f);
+        }
+    } else {
+        float top_z = -INFINITY;
+        for (int e = lane; e < n_experts; e += 32) {
+            top_z = fmaxf(top_z, score[e]);
+        }
+        top_z = pl_warp_max(top_z);
+        float sum = 0.0f;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float x = expf(score[e] - top_z);
+            score[e] = x;
+            sum += x;
+        }
+        sum = pl_warp_sum(sum);
+        for (int e = lane; e < n_experts; e += 32) {
+            const float s = score[e] / sum;
+            score[e] = s;
+            choice[e] = s + (correction != nullptr ? correction[e] : 0.0f);
+        }
     }
     __syncwarp();
     const int per_group = n_experts / n_groups;
     if (keep < n_groups) {
         for (int g = lane; g < n_groups; g += 32) {
-            float best = -INFINITY;
-            for (int j = 0; j < per_group; ++j) {
-                best = fmaxf(best, choice[g * per_group + j]);
+            // the sum of the group's `group_top` largest choice scores (equal scores count once each)
+            float total = 0.0f;
+            int taken[kMaxGroupTop];
+            for (int round = 0; round < min(group_top, per_group); ++round) {
+                float best = -INFINITY;
+                int index = -1;
+                for (int j = 0; j < per_group; ++j) {
+                    bool free = true;
+                    for (int r = 0; r < round; ++r) {
+                        free = free && taken[r] != j;
+                    }
+                    const float x = choice[g * per_group + j];
+                    if (free && (index < 0 || x > best)) {
+                        best = x;
+                        index = j;
+                    }
+                }
+                taken[round] = index;
+                total += best;
             }
-            group_score[g] = best;
+            group_score[g] = total;
         }
         __syncwarp();
         // The `keep` best groups stay (marked +inf as they are picked); the others are shut out.
@@ -244,9 +272,11 @@ __global__ void __launch_bounds__(512, TOKENS > 1 ? 2 : 1) moe_route_kernel(cons
         chosen_sum += score[index];
         __syncwarp();
     }
-    const float inv = 1.0f / (chosen_sum + 1e-20f);
-    for (int j = lane; j < top; j += 32) {
-        weights[static_cast<int64_t>(t) * top + j] *= inv;
+    if (renormalise) {
+        const float inv = 1.0f / (chosen_sum + 1e-20f);
+        for (int j = lane; j < top; j += 32) {
+            weights[static_cast<int64_t>(t) * top + j] *= inv;
+        }
     }
 }
 
@@ -400,6 +430,51 @@ __global__ void moe_gate_up_kernel(const scalar_t* __restrict__ h, int64_t h_str
         const float u = warp_dot<scalar_t>(weights + static_cast<int64_t>(ff + f) * hidden, row, hidden, vectors, lane);
         if (lane == 0) {
             pl_store(act + static_cast<int64_t>(pair) * ff + f, silu_f32(g) * u);
+        }
+    }
+}
+
+// Block (pair, feature block): act[pair, f] = relu(up_e[f] . h)^2, for experts without a gate.
+template <typename scalar_t>
+__global__ void moe_up_kernel(const scalar_t* __restrict__ h, int64_t h_stride, const scalar_t* __restrict__ up,
+                              const int32_t* __restrict__ ids, scalar_t* __restrict__ act, int hidden, int ff, int top,
+                              int n_experts, int vectors) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    extern __shared__ float row[];  // [hidden]
+    const int pair = blockIdx.x;
+    const int t = pair / top;
+    const int e = ids[pair];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        row[i] = pl_load(h + t * h_stride + i);
+    }
+    __syncthreads();
+    if (e < 0 || e >= n_experts) {
+        return;
+    }
+    const scalar_t* weights = up + static_cast<int64_t>(e) * ff * hidden;
+    const int f0 = (blockIdx.y * warps + warp) * kFeaturesPerWarp;
+    if (f0 + kFeaturesPerWarp <= ff) {
+        float u[kFeaturesPerWarp];
+        warp_dots<scalar_t, kFeaturesPerWarp>(weights + static_cast<int64_t>(f0) * hidden, hidden, row, hidden, vectors,
+                                              lane, u);
+        if (lane < kFeaturesPerWarp) {
+            float ul = u[0];
+#pragma unroll
+            for (int r = 1; r < kFeaturesPerWarp; ++r) {
+                ul = lane == r ? u[r] : ul;
+            }
+            ul = fmaxf(ul, 0.0f);
+            pl_store(act + static_cast<int64_t>(pair) * ff + f0 + lane, ul * ul);
+        }
+        return;
+    }
+    for (int f = f0; f < min(f0 + kFeaturesPerWarp, ff); ++f) {
+        float u = warp_dot<scalar_t>(weights + static_cast<int64_t>(f) * hidden, row, hidden, vectors, lane);
+        if (lane == 0) {
+            u = fmaxf(u, 0.0f);
+            pl_store(act + static_cast<int64_t>(pair) * ff + f, u * u);
         }
     }
 }
@@ -607,9 +682,13 @@ __global__ void moe_combine_kernel(const scalar_t* __restrict__ y, const int32_t
 
 // h [T, hidden] (h_stride elements between rows) in the engine's dtype; router fp32 [n_experts,
 // hidden]; correction fp32 [n_experts] or null; ids int32 [T, top]; weights fp32 [T, top].
+// sigmoid_scores: s = sigmoid(z) instead of softmax(z); group_top: how many of a group's largest choice
+// scores add up to its score; renormalise: whether the chosen scores are divided by their sum.
 PL_API int pl_moe_route(const void* h, int64_t h_stride, const float* router, const float* correction, int32_t* ids,
                         float* weights, int n_tokens, int hidden, int n_experts, int top, int n_groups, int keep,
-                        int dtype, cudaStream_t stream) {
+                        int sigmoid_scores, int group_top, int renormalise, int dtype, cudaStream_t stream) {
+    PL_REQUIRE(group_top > 0 && group_top <= kMaxGroupTop, "moe_route: a group's score adds up 1 to %d scores, not %d",
+               kMaxGroupTop, group_top);
     PL_REQUIRE(n_tokens >= 0 && hidden > 0 && n_experts > 0 && top > 0 && n_groups > 0 && keep > 0,
                "moe_route: bad sizes tokens=%d hidden=%d experts=%d top=%d groups=%d keep=%d", n_tokens, hidden,
                n_experts, top, n_groups, keep);
@@ -638,7 +717,7 @@ PL_API int pl_moe_route(const void* h, int64_t h_stride, const float* router, co
             cudaFuncSetAttribute(moe_route_kernel<scalar_t, 8>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
             pl_launch_overlapped(moe_route_kernel<scalar_t, 8>, dim3((n_tokens + 7) / 8), dim3(threads), smem, stream,
                                  static_cast<const scalar_t*>(h), h_stride, router, correction, ids, weights, n_tokens,
-                                 hidden, n_experts, top, n_groups, keep);
+                                 hidden, n_experts, top, n_groups, keep, sigmoid_scores, group_top, renormalise);
         } else {
             if (smem > 48 * 1024) {
                 cudaFuncSetAttribute(moe_route_kernel<scalar_t, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -646,7 +725,7 @@ PL_API int pl_moe_route(const void* h, int64_t h_stride, const float* router, co
             }
             pl_launch_overlapped(moe_route_kernel<scalar_t, 1>, dim3(n_tokens), dim3(threads), smem, stream,
                                  static_cast<const scalar_t*>(h), h_stride, router, correction, ids, weights, n_tokens,
-                                 hidden, n_experts, top, n_groups, keep);
+                                 hidden, n_experts, top, n_groups, keep, sigmoid_scores, group_top, renormalise);
         }
     });
     PL_CHECK_LAUNCH("moe_route");
@@ -676,6 +755,32 @@ PL_API int pl_moe_gate_up(const void* h, int64_t h_stride, const void* gate_up, 
                              static_cast<scalar_t*>(act), hidden, ff, top, n_experts, vectors);
     });
     PL_CHECK_LAUNCH("moe_gate_up");
+    return 0;
+}
+
+// up [n_experts, ff, hidden]; act [T * top, ff] = relu(up_e h)^2 for each pair's expert e.
+PL_API int pl_moe_up(const void* h, int64_t h_stride, const void* up, const int32_t* ids, void* act, int n_tokens,
+                     int hidden, int ff, int top, int n_experts, int dtype, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && hidden > 0 && ff > 0 && top > 0 && n_experts > 0, "moe_up: bad sizes");
+    const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+    PL_REQUIRE(smem <= 200 * 1024, "moe_up: hidden %d is too wide", hidden);
+    if (n_tokens == 0) {
+        return 0;
+    }
+    const int warps = 4;
+    const dim3 grid(n_tokens * top, (ff + warps * kFeaturesPerWarp - 1) / (warps * kFeaturesPerWarp));
+    PL_REQUIRE(grid.y <= 65535, "moe_up: %d features per expert exceed the grid limit", ff);
+    PL_DISPATCH_DTYPE(dtype, "moe_up", {
+        const int vectors = hidden % Vec<scalar_t>::kCount == 0 && (reinterpret_cast<uintptr_t>(up) & 15) == 0;
+        if (smem > 48 * 1024) {
+            cudaFuncSetAttribute(moe_up_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+        }
+        pl_launch_overlapped(moe_up_kernel<scalar_t>, grid, dim3(warps * 32), smem, stream,
+                             static_cast<const scalar_t*>(h), h_stride, static_cast<const scalar_t*>(up), ids,
+                             static_cast<scalar_t*>(act), hidden, ff, top, n_experts, vectors);
+    });
+    PL_CHECK_LAUNCH("moe_up");
     return 0;
 }
 

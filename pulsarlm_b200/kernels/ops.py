@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 25
+ABI_VERSION = 26
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -54,7 +54,7 @@ _SIGNATURES = {
                          _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR, _PTR, _F32, _PTR, _PTR],
     "pl_attention_simt": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                           _I32, _I32, _I32, _I32, _I32, _F32, _F32, _I32, _PTR, _PTR, _PTR, _PTR, _PTR, _I64, _PTR,
-                          _PTR],
+                          _I32, _PTR, _PTR],
     "pl_attention_decode": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
                             _I32, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _PTR, _PTR],
     "pl_attention_decode_mass": [_PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _PTR, _PTR, _I64,
@@ -94,7 +94,15 @@ _SIGNATURES = {
     "pl_short_conv_state_strided": [_PTR, _I64, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
     "pl_gated_delta": [_PTR, _PTR, _PTR, _I64, _PTR, _I64, _PTR, _I64, _PTR, _I64, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR,
                        _PTR, _PTR, _PTR, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _F32, _F32, _F32, _I32, _PTR],
-    "pl_moe_route": [_PTR, _I64, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
+    "pl_moe_route": [_PTR, _I64, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32,
+                     _PTR],
+    "pl_moe_up": [_PTR, _I64, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
+    "pl_pair_embed": [_PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I64, _I64, _I32, _I32,
+                      _PTR, _PTR],
+    "pl_pair_embed_state": [_PTR, _PTR, _PTR, _PTR, _I32, _PTR],
+    "pl_norm_rope_mix_write": [_PTR, _PTR, _PTR, _I64, _PTR, _I64, _F32, _PTR, _PTR, _PTR, _PTR, _I32, _PTR, _PTR,
+                               _I64, _I64, _I32, _I32, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _PTR,
+                               _PTR, _F32, _I32, _PTR, _PTR],
     "pl_moe_gate_up": [_PTR, _I64, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
     "pl_moe_down": [_PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I32, _I32, _I32, _I32, _I32, _I32, _PTR],
     "pl_moe_sort": [_PTR, _I32, _I32, _PTR, _PTR, _PTR, _PTR],
@@ -243,6 +251,73 @@ def take_tokens(tokens: torch.Tensor, source: torch.Tensor, ids: torch.Tensor,
     assert tokens.is_contiguous() and source.is_contiguous() and ids.is_contiguous()
     assert source.numel() <= tokens.numel()
     _call("pl_take_tokens", _p(tokens), _p(source), _p(ids), source.numel(), ids.numel(), _p(status), _stream())
+
+
+def pair_embed(table: torch.Tensor, pairs: torch.Tensor, tokens: torch.Tensor, pos: torch.Tensor, entry: torch.Tensor,
+               slots: torch.Tensor, last_token: torch.Tensor, out: torch.Tensor, mul_prev: int, mul_cur: int,
+               single_tokens: bool, status: torch.Tensor | None = None) -> None:
+    """out[t] (fp32 [T, H]) = table[tokens[t]] + pairs[(before * mul_prev + tokens[t] * mul_cur) mod buckets], with
+    pairs [buckets + 1, H] and its last row for a token at position 0. The token before row t is the row above it
+    where that is the same entry's, else last_token[slots[entry[t]]] (int32, one per request slot), which afterwards
+    holds the entry's last token (single_tokens: every entry brings one token and one launch does both)."""
+    _dev(table, pairs, tokens, pos, entry, slots, last_token, out, status)
+    assert table.is_contiguous() and pairs.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32
+    assert table.dtype == pairs.dtype and table.shape[1] == pairs.shape[1] == out.shape[1] and pairs.shape[0] >= 2
+    for t in (tokens, pos, entry, slots, last_token):
+        assert t.dtype == torch.int32 and t.is_contiguous()
+    n = tokens.numel()
+    assert pos.numel() == n and entry.numel() == n and out.shape[0] == n
+    vocab, hidden = table.shape
+    _call("pl_pair_embed", _p(table), _p(pairs), _p(tokens), _p(pos), _p(entry), _p(slots), _p(last_token), _p(out), n,
+          hidden, vocab, pairs.shape[0] - 1, int(mul_prev), int(mul_cur), int(bool(single_tokens)), _code(table.dtype),
+          _p(status), _stream())
+    if not single_tokens:
+        _call("pl_pair_embed_state", _p(tokens), _p(entry), _p(slots), _p(last_token), n, _stream())
+
+
+NORM_MODES = {"none": 0, "per_head": 1, "whole": 2, "unit_after": 3}
+
+
+def norm_rope_mix_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, v_first: torch.Tensor | None, lam: float,
+                        q_out: torch.Tensor, pos: torch.Tensor, entry: torch.Tensor, table: torch.Tensor,
+                        k_pool: torch.Tensor, v_pool: torch.Tensor, page_size: int, inv_freq: torch.Tensor | None,
+                        rotary: int, mode: str, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+                        eps: float, status: torch.Tensor | None = None) -> None:
+    """q [T, nh, dim], k [T, nkv, dim], v [T, nkv, vdim] (slices of one projection's output: equal row
+    strides) are normed (mode: "none", "per_head" with weights fp32 [dim], "whole" over the whole projection with
+    weights fp32 [nh * dim] and [nkv * dim], "unit_after": per head, no weights, after the rotation), rotated over
+    the first `rotary` columns of every head (inv_freq fp64 [rotary / 2] or None), v mixed with v_first [T, nkv,
+    vdim] as (1 - lam) v + lam v_first (None: not), and written: q to q_out [T, nh, row], k and v into the pools
+    [pages, nkv, page_size, row], all with zeros past their own columns."""
+    _dev(q, k, v, v_first, q_out, pos, entry, table, k_pool, v_pool, inv_freq, q_weight, k_weight, status)
+    tokens, n_heads, dim = q.shape
+    n_kv, vdim = v.shape[1], v.shape[2]
+    row = q_out.shape[2]
+    n_pages = k_pool.shape[0]
+    assert k.shape == (tokens, n_kv, dim) and v.shape[0] == tokens
+    for t_, size in ((q, dim), (k, dim), (v, vdim)):
+        assert t_.stride(2) == 1 and t_.stride(1) == size and (tokens == 1 or t_.stride(0) == q.stride(0))
+        assert t_.dtype == q.dtype
+    assert q_out.shape == (tokens, n_heads, row) and q_out.is_contiguous() and q_out.dtype == q.dtype
+    assert k_pool.shape == (n_pages, n_kv, page_size, row) == v_pool.shape and k_pool.dtype == q.dtype == v_pool.dtype
+    assert k_pool.stride() == v_pool.stride() and k_pool.stride(3) == 1 and k_pool.stride(2) == row
+    v_first_stride = 0
+    if v_first is not None:
+        assert v_first.shape == v.shape and v_first.dtype == q.dtype and v_first.stride(2) == 1
+        assert v_first.stride(1) == vdim
+        v_first_stride = v_first.stride(0)
+    n_q, n_k = (n_heads * dim, n_kv * dim) if mode == "whole" else (dim, dim)
+    for w_, n_ in ((q_weight, n_q), (k_weight, n_k)):
+        assert w_ is None or (w_.dtype == torch.float32 and w_.numel() == n_ and w_.is_contiguous())
+    assert pos.dtype == torch.int32 and entry.dtype == torch.int32 and table.dtype == torch.int32
+    assert pos.numel() == tokens and entry.numel() == tokens and table.dim() == 2 and table.is_contiguous()
+    if inv_freq is not None:
+        assert inv_freq.dtype == torch.float64 and inv_freq.numel() == rotary // 2 and inv_freq.is_contiguous()
+    _call("pl_norm_rope_mix_write", _p(q), _p(k), _p(v), q.stride(0), _p(v_first), v_first_stride, float(lam),
+          _p(q_out), _p(pos), _p(entry), _p(table), table.shape[1], _p(k_pool), _p(v_pool), k_pool.stride(0),
+          k_pool.stride(1), page_size, n_pages, _p(inv_freq), int(rotary) if inv_freq is not None else 0, tokens,
+          n_heads, n_kv, dim, vdim, row, NORM_MODES[mode], _p(q_weight), _p(k_weight), float(eps), _code(q.dtype),
+          _p(status), _stream())
 
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -506,8 +581,11 @@ def gated_delta(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b_pre: torch.
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, top: int, n_groups: int,
-              keep: int) -> tuple[torch.Tensor, torch.Tensor]:
-    """(ids int32 [T, top], weights fp32 [T, top]) of the experts each token's router chooses (see csrc/moe.cu)."""
+              keep: int, sigmoid_scores: bool = False, group_top: int = 1,
+              renormalise: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+    """(ids int32 [T, top], weights fp32 [T, top]) of the experts each token's router chooses (see csrc/moe.cu).
+    sigmoid_scores: scores are sigmoids of the logits instead of their softmax; group_top: how many of a
+    group's largest choice scores add up to its score; renormalise: the chosen scores over their sum."""
     _dev(h, router, correction)
     tokens, hidden = h.shape
     n_experts = router.shape[0]
@@ -517,8 +595,21 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | 
     ids = torch.empty((tokens, top), dtype=torch.int32, device=h.device)
     weights = torch.empty((tokens, top), dtype=torch.float32, device=h.device)
     _call("pl_moe_route", _p(h), h.stride(0) if tokens > 1 else hidden, _p(router), _p(correction), _p(ids),
-          _p(weights), tokens, hidden, n_experts, top, n_groups, keep, _code(h.dtype), _stream())
+          _p(weights), tokens, hidden, n_experts, top, n_groups, keep, int(bool(sigmoid_scores)), int(group_top),
+          int(bool(renormalise)), _code(h.dtype), _stream())
     return ids, weights
+
+
+def moe_up(h: torch.Tensor, up: torch.Tensor, ids: torch.Tensor, act: torch.Tensor) -> None:
+    """act[t * top + j] = relu(Wu h_t)^2 with the weights of expert ids[t, j]; up [E, ff, H] (experts without a gate)."""
+    _dev(h, up, ids, act)
+    tokens, hidden = h.shape
+    n_experts, ff, _ = up.shape
+    top = ids.shape[1]
+    assert up.is_contiguous() and up.shape[2] == hidden and up.dtype == h.dtype == act.dtype
+    assert act.is_contiguous() and act.shape == (tokens * top, ff) and ids.is_contiguous() and h.stride(1) == 1
+    _call("pl_moe_up", _p(h), h.stride(0) if tokens > 1 else hidden, _p(up), _p(ids), _p(act), tokens, hidden, ff, top,
+          n_experts, _code(h.dtype), _stream())
 
 
 def moe_gate_up(h: torch.Tensor, gate_up: torch.Tensor, ids: torch.Tensor, act: torch.Tensor) -> None:
@@ -876,15 +967,22 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                    pos: torch.Tensor, entry: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
                    scale: float, status: torch.Tensor | None = None, mass_sum: torch.Tensor | None = None,
                    weight_sum: torch.Tensor | None = None, query_weights: torch.Tensor | None = None,
-                   softcap: float = 0.0, sinks: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> None:
+                   softcap: float = 0.0, sinks: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                   distance_bias: torch.Tensor | None = None) -> None:
     """Causal paged attention; q and out [T, nh, hd] (row strides free), pools
     [pages, nkv, page_size, hd]. With mass_sum fp32 [pages, nh] and weight_sum fp32
     [pages], the attention mass of every attended page is added to them
     (query_weights fp32 [T], all 1 when None). softcap > 0: scaled scores pass through
     softcap * tanh(s / softcap) before the softmax. sinks fp32 [nh]: exp(sinks[h]) joins head
     h's softmax denominator (a term with no key and no value). gate [T, nh] logits (row
-    stride free): head h's output for token t is multiplied by sigmoid(gate[t, h])."""
-    _dev(q, k_pool, v_pool, table, pos, entry, out, status, mass_sum, weight_sum, query_weights, sinks, gate)
+    stride free): head h's output for token t is multiplied by sigmoid(gate[t, h]). distance_bias
+    fp32 [rows, nh]: row min(distance, rows - 1) of it is added to the scaled scores of a key
+    `distance` tokens before the query."""
+    _dev(q, k_pool, v_pool, table, pos, entry, out, status, mass_sum, weight_sum, query_weights, sinks, gate,
+         distance_bias)
+    if distance_bias is not None:
+        assert distance_bias.dtype == torch.float32 and distance_bias.dim() == 2 and distance_bias.is_contiguous()
+        assert distance_bias.shape[1] == q.shape[1] and distance_bias.shape[0] > 0
     if sinks is not None:
         assert sinks.dtype == torch.float32 and sinks.shape == (q.shape[1],) and sinks.is_contiguous()
     if gate is not None:
@@ -908,7 +1006,8 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
           page_size, n_pages, _p(table), table.shape[1], _p(pos), _p(entry), _p(out), out.stride(0), tokens,
           n_heads, n_kv, head_dim, int(window or 0), float(scale), float(softcap or 0.0), _code(q.dtype),
           _p(mass_sum), _p(weight_sum), _p(query_weights), _p(sinks), _p(gate),
-          gate.stride(0) if gate is not None else 0, _p(status), _stream())
+          gate.stride(0) if gate is not None else 0, _p(distance_bias),
+          distance_bias.shape[0] if distance_bias is not None else 0, _p(status), _stream())
 
 
 def attention_decode_supports(head_dim: int, group: int, page_size: int, dtype: torch.dtype) -> bool:
@@ -997,26 +1096,32 @@ def attention_decode_ctas_per_sm(head_dim: int) -> int:
 
 class _AttentionExtras(ctypes.Structure):
     _fields_ = [("sinks", _PTR), ("gate", _PTR), ("gate_row_stride", _I64), ("split_weights", _I32),
-                ("softcap", _F32)]
+                ("softcap", _F32), ("distance_bias", _PTR), ("bias_rows", _I32)]
 
 
 def attention_extras(q: torch.Tensor, sinks: torch.Tensor | None, gate: torch.Tensor | None,
-                     split_weights: bool, softcap: float = 0.0) -> "_AttentionExtras | None":
+                     split_weights: bool, softcap: float = 0.0,
+                     distance_bias: torch.Tensor | None = None) -> "_AttentionExtras | None":
     """What the tensor-core attention kernels take beyond plain softmax attention (the struct
     PlAttentionExtras): sinks fp32 [nh] (exp(sinks[h]) joins head h's denominator), gate [T, nh]
     logits in q's dtype (outputs times their sigmoid), split_weights (softmax weights enter the
     value product as two bfloat16 terms), softcap (> 0: scaled scores pass through softcap *
-    tanh(s / softcap)). None when nothing is asked for. The tensors must outlive the call that
-    takes the struct."""
-    if sinks is None and gate is None and not split_weights and not softcap:
+    tanh(s / softcap)), distance_bias fp32 [rows, nh] (row min(distance, rows - 1) joins the scaled
+    scores of a key `distance` tokens before the query). None when nothing is asked for. The tensors
+    must outlive the call that takes the struct."""
+    if sinks is None and gate is None and not split_weights and not softcap and distance_bias is None:
         return None
-    _dev(sinks, gate)
+    _dev(sinks, gate, distance_bias)
+    if distance_bias is not None:
+        assert distance_bias.dtype == torch.float32 and distance_bias.dim() == 2 and distance_bias.is_contiguous()
+        assert distance_bias.shape[1] == q.shape[1] and distance_bias.shape[0] > 0
     if sinks is not None:
         assert sinks.dtype == torch.float32 and sinks.shape == (q.shape[1],) and sinks.is_contiguous()
     if gate is not None:
         assert gate.dtype == q.dtype and gate.shape == (q.shape[0], q.shape[1]) and gate.stride(1) == 1
     return _AttentionExtras(_p(sinks), _p(gate), gate.stride(0) if gate is not None else 0, int(bool(split_weights)),
-                            float(softcap or 0.0))
+                            float(softcap or 0.0), _p(distance_bias),
+                            distance_bias.shape[0] if distance_bias is not None else 0)
 
 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,

@@ -1,3 +1,3 @@
 """Architectures: importing this package registers every one of them."""
 
-from . import bunosun, llama, rerilorn, simetar  # noqa: F401
+from . import bunosun, llama, puvirax, rerilorn, simetar  # noqa: F401

@@ -120,6 +120,9 @@ class Model:
         # The cache units, in the order the cache manager hears of them: one per layer, or
         # (spec.cache_per_run) one per entry of the order. `_unit_layer[u]` is the layer of unit u.
         self._unit_layer = list(spec.order) if spec.cache_per_run else list(range(len(spec.layers)))
+        # Parts outside the layers that keep something per request (an embedding that remembers a
+        # request's last token): their needs follow the layers' in `cache_needs()`.
+        self._own_holders = [part for part in (self.embedding,) if hasattr(part, "cache_need")]
         self._run_bindings: list | None = None
         self._rejoin = frozenset(int(r) for r in spec.rejoin_runs)
         for r in self._rejoin:
@@ -148,19 +151,22 @@ class Model:
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> list:
         """Per layer: the mixer's KVCacheNeed, StateNeed or None; for a block whose other
-        parts keep state too (`cache_holders()`), a tuple with every holder's need."""
+        parts keep state too (`cache_holders()`), a tuple with every holder's need. After the
+        layers: one need for every part outside them that keeps something per request."""
         out = []
         for layer in self._unit_layer:
             b = self.blocks[layer]
             holders = getattr(b, "cache_holders", None)
             out.append(tuple(h.cache_need() for h in holders()) if holders is not None else b.mixer.cache_need())
-        return out
+        return out + [part.cache_need() for part in self._own_holders]
 
     def cache_holder(self, key):
         """The part behind a cache manager's holder key: a layer's mixer, or for the key
         (layer, place) that place among the block's cache holders."""
         if isinstance(key, tuple):
             return self.blocks[self._unit_layer[key[0]]].cache_holders()[key[1]]
+        if key >= len(self._unit_layer):
+            return self._own_holders[key - len(self._unit_layer)]
         return self.blocks[self._unit_layer[key]].mixer
 
     def cache_sources(self) -> list[int | None]:
@@ -210,13 +216,15 @@ class Model:
             b.mixer.bind_cache(mine[0] if isinstance(mine, list) else mine)
 
     def bind_caches(self, bindings: list) -> None:
+        for place, part in enumerate(self._own_holders):
+            part.bind_cache(bindings[len(self._unit_layer) + place])
         if self.spec.cache_per_run:
             # One binding per run: a block is pointed at its run's cache right before it runs
             # (`forward`); here each block gets the binding of its first run, so that whatever the
             # parts derive from a binding (page size, kernels' shapes) is known before a step.
             if any(getattr(b.mixer, "cache_from", None) is not None for b in self.blocks):
                 raise ValueError("a model that keeps a cache per run cannot have layers that read another's cache")
-            self._run_bindings = list(bindings)
+            self._run_bindings = list(bindings[: len(self._unit_layer)])
             seen = set()
             for run, layer in enumerate(self.spec.order):
                 if layer not in seen:

@@ -238,6 +238,10 @@ class Attention(Part):
                       if self.sink_logit is not None else None)
         self.q_norm: torch.Tensor | None = None
         self.k_norm: torch.Tensor | None = None
+        # fp32 [rows, n_heads], set by a mixer that has one: row min(distance, rows - 1) joins the scaled
+        # scores of a key `distance` tokens before the query
+        self.distance_bias: torch.Tensor | None = None
+        self.head_gate = False  # (a mixer that multiplies every head's output by a sigmoid hands `attend` the logits)
         self.position = build_part("position", self.param("position"), ctx)
         self.qkv: torch.Tensor | None = None
         self.o: torch.Tensor | None = None
@@ -436,10 +440,10 @@ class Attention(Part):
         return self._kernels(self.ctx.dtype)[0]
 
     def _wants_extras(self) -> bool:
-        """A score cap or a sink term: the tensor-core kernels take them in their build with
-        extras (csrc/attention_decode.cu, attention_prefill.cu), without work lists, wide tiles
-        or attention mass."""
-        return bool(self.softcap) or self.sinks is not None
+        """A score cap, a sink term, a bias by distance or a gate per head: the tensor-core kernels
+        take them in their build with extras (csrc/attention_decode.cu, attention_prefill.cu),
+        without work lists, wide tiles or attention mass."""
+        return bool(self.softcap) or self.sinks is not None or self.distance_bias is not None or self.head_gate
 
     def plan_key(self):
         """Layers of equal tiling share one plan: the tile lists depend on the kernels'
@@ -535,14 +539,17 @@ class Attention(Part):
             plan["tiles_wide"] = np.array(wide_tiles, dtype=np.int32).reshape(len(wide_tiles), 4)
         return plan
 
-    def _attend_with_extras(self, q, out, table, batch, plan, decode_kernel: bool, prefill_kernel: bool) -> None:
-        """Attention with a score cap and / or a sink term. bfloat16 shapes the tensor-core
+    def _attend_with_extras(self, q, out, table, batch, plan, decode_kernel: bool, prefill_kernel: bool,
+                            gate: torch.Tensor | None = None) -> None:
+        """Attention with a score cap, a sink term, a bias by distance and / or a gate per head
+        (`gate`: [T, n_heads] logits). bfloat16 shapes the tensor-core
         kernels take: the leading single tokens on the split-key kernel, prompt portions on
-        the tiled mma.sync kernel, both in their build with extras (the cap on every score
-        in fp32, the sink in the row's last step, softmax weights in two bfloat16 terms);
+        the tiled mma.sync kernel, both in their build with extras (cap and bias on every score
+        in fp32, sink and gate in the row's last step, softmax weights in two bfloat16 terms);
         everything else on the CUDA-core kernel."""
         cache = self.cache
         tokens = q.shape[0]
+        bias = self.distance_bias
         n_decode = min(int(batch.n_decode), tokens) if decode_kernel else 0
         if n_decode > 0:
             max_context = plan.get("max_context") or max(batch.host_context_lens[:n_decode])
@@ -558,7 +565,9 @@ class Attention(Part):
             ops.attention_decode(q[:n_decode], cache.k_pool, cache.v_pool, table, batch.pos[:n_decode],
                                  batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window, self.scale,
                                  splits, scratch, batch.status,
-                                 extras=ops.attention_extras(q[:n_decode], self.sinks, None, True, self.softcap))
+                                 extras=ops.attention_extras(q[:n_decode], self.sinks,
+                                                             gate[:n_decode] if gate is not None else None, True,
+                                                             self.softcap, bias))
         if n_decode == tokens:
             return
         tiles = plan.get("tiles")
@@ -566,14 +575,16 @@ class Attention(Part):
             # (the tile list covers exactly the tokens after the leading single tokens)
             ops.attention_prefill(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size, self.window,
                                   self.scale, batch.status,
-                                  extras=ops.attention_extras(q, self.sinks, None, True, self.softcap))
+                                  extras=ops.attention_extras(q, self.sinks, gate, True, self.softcap, bias))
             return
         ops.attention_simt(q[n_decode:], cache.k_pool, cache.v_pool, table, batch.pos[n_decode:],
                            batch.entry[n_decode:], out[n_decode:], cache.page_size, self.window, self.scale,
-                           batch.status, softcap=self.softcap, sinks=self.sinks)
+                           batch.status, softcap=self.softcap, sinks=self.sinks,
+                           gate=gate[n_decode:] if gate is not None else None, distance_bias=bias)
 
-    def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch, rope: tuple | None = None) -> None:
-        """out = attention of q over the cache. The batch's leading `n_decode` tokens
+    def attend(self, q: torch.Tensor, out: torch.Tensor, table: torch.Tensor, batch, rope: tuple | None = None,
+               gate: torch.Tensor | None = None) -> None:
+        """out = attention of q over the cache (`gate`: logits [T, n_heads] of a mixer with `head_gate`). The batch's leading `n_decode` tokens
         are single tokens of their requests: in bfloat16 they go to the split-key
         tensor-core kernel and prompt portions to the tiled tensor-core kernel (tcgen05
         when the cache layout allows TMA, else mma.sync) when those take the shape;
@@ -609,7 +620,7 @@ class Attention(Part):
             group = self.n_heads // self.n_kv
             wide = group % 2 == 1 and plan.get("tiles_wide") is not None
             tiles = plan.get("tiles_wide") if wide else plan.get("tiles")
-            fast = (not self.softcap and self.sinks is None and tiles is not None and n_single < tokens and self._kernels(q.dtype)[1]
+            fast = (not self._wants_extras() and tiles is not None and n_single < tokens and self._kernels(q.dtype)[1]
                     and ops.attention_prefill_tcgen05_measures_mass(group, cache.page_size, wide)
                     and ops.attention_prefill_tcgen05_supports(q, cache.k_pool, cache.page_size))
             n_simt = n_single if fast else tokens
@@ -617,7 +628,8 @@ class Attention(Part):
                 ops.attention_simt(q[:n_simt], cache.k_pool, cache.v_pool, table, batch.pos[:n_simt],
                                    batch.entry[:n_simt], out[:n_simt], cache.page_size, self.window, self.scale,
                                    batch.status, cache.mass_sum, cache.weight_sum, weights[:n_simt],
-                                   softcap=self.softcap, sinks=self.sinks)
+                                   softcap=self.softcap, sinks=self.sinks,
+                                   gate=gate[:n_simt] if gate is not None else None, distance_bias=self.distance_bias)
             if fast:
                 ops.attention_prefill_tcgen05(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size,
                                               self.window, self.scale, batch.status, 1, None, wide,
@@ -626,7 +638,7 @@ class Attention(Part):
         plan = batch.plans.get(self.plan_key()) or {}
         decode_kernel, prefill_kernel = self._kernels(q.dtype)
         if self._wants_extras():
-            self._attend_with_extras(q, out, table, batch, plan, decode_kernel, prefill_kernel)
+            self._attend_with_extras(q, out, table, batch, plan, decode_kernel, prefill_kernel, gate)
             return
         n_decode = min(int(batch.n_decode), tokens) if decode_kernel else 0
         if n_decode > 0 and plan.get("decode_items") is not None:

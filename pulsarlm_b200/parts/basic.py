@@ -14,7 +14,7 @@ import torch
 from ..kernels import ops
 from .linear import activated_linear, gated_feed_forward, linear
 from .registry import BuildContext, Part, register_part
-from .spec import PartSpec, TensorNeed
+from .spec import PartSpec, StateNeed, TensorNeed
 
 
 @dataclasses.dataclass
@@ -322,9 +322,60 @@ class Embedding(Part):
         return x
 
 
+@register_part("embedding", "pair_hash_table")
+class PairHashEmbedding(Part):
+    """x[t] = weight[token[t]] + pairs[(before * mul_prev + token[t] * mul_cur) mod buckets] in fp32,
+    where `before` is the token ahead of token[t] in its sequence; a sequence's first token
+    takes the last row of `pairs` (row number `buckets`). The token before a step's first token
+    is part of the request's state: one int32 per request slot, which the kernel reads for an
+    entry's first row and moves on to the entry's last token. params: vocab_size, hidden_size,
+    buckets, mul_prev, mul_cur. tensors: weight [vocab, hidden], pairs [buckets + 1, hidden]."""
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.vocab = int(self.param("vocab_size"))
+        self.hidden = int(self.param("hidden_size"))
+        self.buckets = int(self.param("buckets"))
+        self.mul_prev = int(self.param("mul_prev"))
+        self.mul_cur = int(self.param("mul_cur"))
+        if self.buckets <= 0:
+            raise ValueError(f"pair_hash_table: buckets must be positive, got {self.buckets}")
+        self.weight: torch.Tensor | None = None
+        self.pairs: torch.Tensor | None = None
+        self.binding = None
+
+    @classmethod
+    def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
+        p = spec.params
+        return {spec.tensors["weight"]: TensorNeed((int(p["vocab_size"]), int(p["hidden_size"]))),
+                spec.tensors["pairs"]: TensorNeed((int(p["buckets"]) + 1, int(p["hidden_size"])))}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.spec.tensors["weight"]].contiguous()
+        self.pairs = tensors[self.spec.tensors["pairs"]].contiguous()
+
+    def cache_need(self) -> StateNeed:
+        return StateNeed((1,), "int32")
+
+    def bind_cache(self, binding) -> None:
+        self.binding = binding
+
+    def captures_state_steps(self) -> bool:
+        return True  # (a step of single tokens reads and moves the slots on in one launch, nothing on the host)
+
+    def forward(self, tokens: torch.Tensor, batch=None) -> torch.Tensor:
+        if batch is None or self.binding is None:
+            raise ValueError("pair_hash_table: the embedding needs the step (positions, entries, state slots)")
+        x = torch.empty((tokens.numel(), self.hidden), dtype=torch.float32, device=tokens.device)
+        ops.pair_embed(self.weight, self.pairs, tokens, batch.pos, batch.entry, batch.slots, self.binding.states.view(-1),
+                       x, self.mul_prev, self.mul_cur, int(batch.n_decode) == tokens.numel(), batch.status)
+        return x
+
+
 @register_part("head", "linear")
 class Head(Part):
-    """logits = h W^T in fp32. params: vocab_size, hidden_size. tensors: weight
+    """logits = h W^T in fp32, times `scale` where given. params: vocab_size, hidden_size, scale
+    (optional, 1 when absent). tensors: weight
     [vocab, hidden], or None for a head tied to the embedding table, which the
     model then hands over with `tie`. The reference ties when the weights hold
     no lm_head.weight (pulsarlm-core/src/engine/model/llama.cpp:31); here
@@ -334,6 +385,7 @@ class Head(Part):
         super().__init__(spec, ctx)
         self.vocab = int(self.param("vocab_size"))
         self.hidden = int(self.param("hidden_size"))
+        self.scale = float(spec.params.get("scale") or 1.0)
         self.weight: torch.Tensor | None = None
 
     @property
@@ -361,7 +413,10 @@ class Head(Part):
         self.weight = table
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return linear(h, self.weight, out_dtype=torch.float32)
+        logits = linear(h, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            logits.mul_(self.scale)
+        return logits
 
 
 @register_part("feed_forward", "gated_mlp")

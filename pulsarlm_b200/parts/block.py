@@ -20,24 +20,29 @@ from .spec import LayerSpec
 class PreNormBlock:
     """x += mixer(norm_mixer(x)); x += feed_forward(norm_ff(x))
     (pulsarlm-core/src/engine/model/llama.cpp:88-92). Norm names in the
-    LayerSpec: "mixer" and "feed_forward"."""
+    LayerSpec: "mixer" and "feed_forward". A LayerSpec whose feed_forward is None has
+    the first line only."""
 
     def __init__(self, spec: LayerSpec, ctx: BuildContext):
         self.spec = spec
         self.mixer_norm = build_part("norm", spec.norms["mixer"], ctx)
         self.mixer = build_part("mixer", spec.mixer, ctx)
-        self.ff_norm = build_part("norm", spec.norms["feed_forward"], ctx)
-        self.feed_forward = build_part("feed_forward", spec.feed_forward, ctx)
+        self.ff_norm = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.ff_norm = build_part("norm", spec.norms["feed_forward"], ctx)
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, ctx)
         self._native: bool | None = None  # whether the parts are the ones the native layer call takes
 
     @classmethod
     def part_specs(cls, spec: LayerSpec):
         """(kind, PartSpec) of every part, so tensor needs can be listed without building."""
-        return [("norm", spec.norms["mixer"]), ("mixer", spec.mixer),
-                ("norm", spec.norms["feed_forward"]), ("feed_forward", spec.feed_forward)]
+        out = [("norm", spec.norms["mixer"]), ("mixer", spec.mixer)]
+        if spec.feed_forward is not None:
+            out += [("norm", spec.norms["feed_forward"]), ("feed_forward", spec.feed_forward)]
+        return out
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward]
+        return [p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None]
 
     def forward(self, x: torch.Tensor, delta: torch.Tensor | None, batch) -> tuple[torch.Tensor, torch.Tensor]:
         # The standard parts in bfloat16: the whole layer from one native call (the same kernels
@@ -50,6 +55,8 @@ class PreNormBlock:
                 return done
         h = self.mixer_norm.forward(x, delta)
         mixed = self.mixer.forward(h, batch)
+        if self.feed_forward is None:
+            return x, mixed
         h = self.ff_norm.forward(x, mixed)
         return x, self.feed_forward.forward(h, batch)
 

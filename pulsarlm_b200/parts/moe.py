@@ -1,5 +1,5 @@
-"""A routed feed-forward: many small gated feed-forwards of which each token uses a few,
-chosen by a router, beside an optional one that every token uses."""
+"""A routed feed-forward: many small feed-forwards (gated, or plain with the square of relu)
+of which each token uses a few, chosen by a router, beside an optional one that every token uses."""
 
 from __future__ import annotations
 
@@ -8,7 +8,7 @@ import os
 import torch
 
 from ..kernels import ops
-from .linear import gated_feed_forward, linear
+from .linear import activated_linear, gated_feed_forward, linear
 from .registry import BuildContext, Part, register_part
 from .spec import PartSpec, TensorNeed
 
@@ -34,8 +34,14 @@ class RoutedExperts(Part):
     No step asks the host which experts were chosen, so steps of single tokens can be
     captured.
 
+    Variants, all parameters: `scores` = "sigmoid" makes s the sigmoid of every logit alone
+    (default "softmax"); `group_top` = n makes a group's score the sum of its n largest choice
+    scores (default 1); `renormalise` = False leaves the chosen scores as the weights (default
+    True); `expert` = "relu2" makes every expert, and the shared one, W_down relu(W_up h)^2 without
+    a gate (default "gated_silu"; such experts have no `expert_gate` / `shared_gate` tensors).
+
     params: hidden_size, expert_size, n_experts, top, groups (default 1), keep_groups
-    (default groups), shared_size (optional). tensors: router [E, H], correction [E]
+    (default groups), shared_size (optional), scores, group_top, renormalise, expert. tensors: router [E, H], correction [E]
     (optional), experts: a name pattern with `{e}` for gate / up / down
     (`expert_gate`, `expert_up` [F, H], `expert_down` [H, F]), shared_gate, shared_up [Fs, H],
     shared_down [H, Fs]."""
@@ -50,13 +56,17 @@ class RoutedExperts(Part):
         self.groups = int(p.get("groups") or 1)
         self.keep = int(p.get("keep_groups") or self.groups)
         self.shared_size = int(p["shared_size"]) if p.get("shared_size") else 0
+        self.sigmoid_scores = {"softmax": False, "sigmoid": True}[str(p.get("scores") or "softmax")]
+        self.group_top = int(p.get("group_top") or 1)
+        self.renormalise = bool(p.get("renormalise", True))
+        self.gated = {"gated_silu": True, "relu2": False}[str(p.get("expert") or "gated_silu")]
         if self.n_experts % self.groups or not 0 < self.keep <= self.groups:
             raise ValueError(f"moe: {self.n_experts} experts in {self.groups} groups of which {self.keep} stay")
         if not 0 < self.top <= self.keep * (self.n_experts // self.groups):
             raise ValueError(f"moe: {self.top} experts cannot be chosen from {self.keep} groups of "
                              f"{self.n_experts // self.groups}")
         self.router = self.correction = None
-        self.gate_up = self.down = None            # [E, 2F, H], [E, H, F]
+        self.gate_up = self.down = None            # [E, 2F, H] ([E, F, H] without a gate), [E, H, F]
         self.gate_up_t = self.down_t = None        # the same with rows and columns swapped, for the grouped products
         self.shared_gate_up = self.shared_down = None
 
@@ -64,16 +74,19 @@ class RoutedExperts(Part):
     def tensor_needs(cls, spec: PartSpec) -> dict[str, TensorNeed]:
         p, t = spec.params, spec.tensors
         h, f, e = int(p["hidden_size"]), int(p["expert_size"]), int(p["n_experts"])
+        gated = str(p.get("expert") or "gated_silu") == "gated_silu"
         needs = {t["router"]: TensorNeed((e, h))}
         if t.get("correction"):
             needs[t["correction"]] = TensorNeed((e,), role="offset")
         for i in range(e):
-            needs[t["expert_gate"].format(e=i)] = TensorNeed((f, h))
+            if gated:
+                needs[t["expert_gate"].format(e=i)] = TensorNeed((f, h))
             needs[t["expert_up"].format(e=i)] = TensorNeed((f, h))
             needs[t["expert_down"].format(e=i)] = TensorNeed((h, f))
         if p.get("shared_size"):
             fs = int(p["shared_size"])
-            needs[t["shared_gate"]] = TensorNeed((fs, h))
+            if gated:
+                needs[t["shared_gate"]] = TensorNeed((fs, h))
             needs[t["shared_up"]] = TensorNeed((fs, h))
             needs[t["shared_down"]] = TensorNeed((h, fs))
         return needs
@@ -83,11 +96,16 @@ class RoutedExperts(Part):
         self.router = tensors[t["router"]].float().contiguous()
         self.correction = tensors[t["correction"]].float().contiguous() if t.get("correction") else None
         experts = range(self.n_experts)
-        self.gate_up = torch.stack([torch.cat([tensors[t["expert_gate"].format(e=i)],
-                                               tensors[t["expert_up"].format(e=i)]], dim=0) for i in experts]).contiguous()
+        if self.gated:
+            self.gate_up = torch.stack([torch.cat([tensors[t["expert_gate"].format(e=i)],
+                                                   tensors[t["expert_up"].format(e=i)]], dim=0)
+                                        for i in experts]).contiguous()
+        else:
+            self.gate_up = torch.stack([tensors[t["expert_up"].format(e=i)] for i in experts]).contiguous()
         self.down = torch.stack([tensors[t["expert_down"].format(e=i)] for i in experts]).contiguous()
         if self.shared_size:
-            self.shared_gate_up = torch.cat([tensors[t["shared_gate"]], tensors[t["shared_up"]]], dim=0).contiguous()
+            self.shared_gate_up = (torch.cat([tensors[t["shared_gate"]], tensors[t["shared_up"]]], dim=0).contiguous()
+                                   if self.gated else tensors[t["shared_up"]].contiguous())
             self.shared_down = tensors[t["shared_down"]].contiguous()
 
     def _grouped(self, h: torch.Tensor) -> bool:
@@ -96,8 +114,13 @@ class RoutedExperts(Part):
 
     def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
         tokens = h.shape[0]
-        ids, weights = ops.moe_route(h, self.router, self.correction, self.top, self.groups, self.keep)
-        shared = gated_feed_forward(h, self.shared_gate_up, self.shared_down) if self.shared_size else None
+        ids, weights = ops.moe_route(h, self.router, self.correction, self.top, self.groups, self.keep,
+                                     self.sigmoid_scores, self.group_top, self.renormalise)
+        shared = None
+        if self.shared_size and self.gated:
+            shared = gated_feed_forward(h, self.shared_gate_up, self.shared_down)
+        elif self.shared_size:
+            shared = activated_linear(linear(h, self.shared_gate_up), None, "relu2", self.shared_down)
         out = torch.empty((tokens, self.hidden), dtype=h.dtype, device=h.device)
         if self._grouped(h):
             # Pairs in expert order; each projection one grouped product over the sorted rows (the
@@ -106,11 +129,17 @@ class RoutedExperts(Part):
             x = ops.moe_gather(h, pair_of_row, self.top)
             gate_up = torch.nn.functional.grouped_mm(x, self.gate_up.transpose(1, 2), offs=ends)
             act = torch.empty((x.shape[0], self.ff), dtype=h.dtype, device=h.device)
-            ops.swiglu(gate_up, act)
+            if self.gated:
+                ops.swiglu(gate_up, act)
+            else:
+                ops.bias_act(gate_up, None, act, "relu2")
             y = torch.nn.functional.grouped_mm(act, self.down.transpose(1, 2), offs=ends)
             ops.moe_combine(y, row_of_pair, weights, shared, out)
             return out
         act = torch.empty((tokens * self.top, self.ff), dtype=h.dtype, device=h.device)
-        ops.moe_gate_up(h, self.gate_up, ids, act)
+        if self.gated:
+            ops.moe_gate_up(h, self.gate_up, ids, act)
+        else:
+            ops.moe_up(h, self.gate_up, ids, act)
         ops.moe_down(act, self.down, ids, weights, shared, out)
         return out

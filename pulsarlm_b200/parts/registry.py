@@ -73,7 +73,7 @@ def _load_builtins() -> None:
     if not _builtins_loaded:
         _builtins_loaded = True
         from . import (attention, basic, block, conv_attention, delta_rule, diff_attention, gated_delta,  # noqa: F401
-                       latent_attention, moe, short_conv)
+                       latent_attention, moe, normed_attention, short_conv)
 
 
 def part_class(kind: str, name: str) -> type:
