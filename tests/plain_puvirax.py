@@ -15,6 +15,11 @@ import math
 import torch
 
 
+def relative_error_of(got: torch.Tensor, want: torch.Tensor) -> float:
+    """Largest |difference| over largest |wanted|."""
+    return float((got.double() - want.double()).abs().max() / want.double().abs().max().clamp(min=1e-30))
+
+
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
