@@ -969,6 +969,165 @@ def simetar_kernels(width: int, pk: dict) -> dict:
     return out
 
 
+def puvirax_config(width: int, layers: int, vocab: int = 32000) -> dict:
+    """A Puvirax model at a real model's layer sizes: heads of 64 in groups of four throughout; the layers
+    cycle through attention with a norm over the whole q and k projections and a bias by distance (32 rows
+    reaching 4,096 tokens back) over a dense feed-forward of 4 x width, rotary attention (half of every head
+    rotated, frequency bands, unit q and k, a gate per head) over routed experts (16 of size width in 4 groups
+    of which 2 stay, 2 chosen, beside a shared expert of 2 x width: the active parameters of the dense layer),
+    rotary attention over a dense feed-forward, and attention with a norm per head, the same kind of bias and a
+    window of 1,024 over routed experts. Every layer mixes its values with the first layer's. A pair table of
+    65,521 rows; the head is the embedding table."""
+    heads, kv = width // 64, max(1, width // 256)
+    dense = {"kind": "dense", "ff": 4 * width}
+    routed = {"kind": "moe", "expert": {"ff": width}, "shared": {"ff": 2 * width},
+              "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    base = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 64, "scale": 0.125, "v_mix": True}
+    rot = {"base": 500000.0, "dims": 32, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    biased = {**base, "bias_max": 4096, "bias_rows": 32}
+    cycle = [{"type": "attention_3", "mixer": biased, "mlp": dense},
+             {"type": "attention", "mixer": {**base, "rot": rot}, "mlp": routed},
+             {"type": "attention", "mixer": {**base, "rot": rot}, "mlp": dense},
+             {"type": "attention_2", "mixer": {**biased, "mask": {"size": 1024}}, "mlp": routed}]
+    return {"architecture": "Puvirax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": [cycle[i % 4] for i in range(layers)]}
+
+
+def puvirax_kernels(width: int, pk: dict) -> dict:
+    """The Puvirax design's kernels alone at one layer's sizes, each beside the like kernel of the Llama layer
+    (or, for the router and the experts, of the Bunosun layer): milliseconds, algorithmic bytes or FLOPs,
+    fraction of the copy bandwidth."""
+    import torch
+
+    from pulsarlm_b200.kernels import ops
+    from pulsarlm_b200.parts.normed_attention import bias_by_distance
+
+    dev, bf = "cuda:0", torch.bfloat16
+    out: dict = {}
+
+    def note(name, ms, nbytes=None, flops=None):
+        out[name] = {"ms": ms}
+        if nbytes is not None:
+            out[name].update(bytes=nbytes, frac_of_hbm=nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"])
+        if flops is not None:
+            out[name].update(tflops=flops / (ms / 1e3) / 1e12, frac_of_bf16=flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"])
+
+    heads, kv, hd, page, vocab, buckets = width // 64, max(1, width // 256), 64, 16, 32000, 65521
+    experts, top, ff = 16, 2, width
+    table_w = torch.randn((vocab, width), device=dev).to(bf)
+    pairs_w = torch.randn((buckets + 1, width), device=dev).to(bf)
+    router = torch.randn((experts, width), device=dev)
+    correction = torch.randn(experts, device=dev) * 0.1
+    gate_up = torch.randn((experts, 2 * ff, width), device=dev).to(bf)
+    up, down = gate_up[:, :ff].contiguous(), torch.randn((experts, width, ff), device=dev).to(bf)
+    for tokens, entries in ((2048, 1), (8, 8), (64, 64)):
+        tag = f"T{tokens}_E{entries}"
+        per = tokens // entries
+        entry = torch.arange(entries, dtype=torch.int32, device=dev).repeat_interleave(per)
+        slots = torch.arange(entries, dtype=torch.int32, device=dev)
+        pos = torch.arange(1, per + 1, dtype=torch.int32, device=dev).repeat(entries)
+        n_pages = entries * ((per + 1) // page + 1)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(entries, -1)
+        ids = torch.randint(0, vocab, (tokens,), dtype=torch.int32, device=dev)
+        x = torch.empty((tokens, width), device=dev)
+        last = torch.zeros(entries + 1, dtype=torch.int32, device=dev)
+        note(f"pair_embed_{tag}", time_kernel(lambda: ops.pair_embed(table_w, pairs_w, ids, pos, entry, slots, last, x,
+                                                                    1000003, 31, per == 1)), tokens * width * (2 + 2 + 4))
+        note(f"embed_{tag} (Llama)", time_kernel(lambda: ops.embed(table_w, ids, x)), tokens * width * (2 + 4))
+        # projection -> norms, rotation, value mixing, cache write
+        proj = torch.randn((tokens, (heads + 2 * kv) * hd + 8), device=dev).to(bf)
+        q_end, k_end, v_end = heads * hd, (heads + kv) * hd, (heads + 2 * kv) * hd
+        q, k, v = (proj[:, :q_end].view(tokens, heads, hd), proj[:, q_end:k_end].view(tokens, kv, hd),
+                   proj[:, k_end:v_end].view(tokens, kv, hd))
+        first = torch.randn((tokens, kv, hd), device=dev).to(bf)
+        pools = torch.zeros((2, n_pages, kv, page, hd), dtype=bf, device=dev)
+        q_out = torch.empty((tokens, heads, hd), dtype=bf, device=dev)
+        inv = torch.rand(hd // 4, dtype=torch.float64, device=dev)
+        moved = tokens * ((heads + 3 * kv) * hd * 2 + (heads + 2 * kv) * hd * 2)
+        for mode, wq, wk, rot in (("unit_after", None, None, inv), ("per_head", torch.ones(hd, device=dev), torch.ones(hd, device=dev), None),
+                                  ("whole", torch.ones(heads * hd, device=dev), torch.ones(kv * hd, device=dev), None)):
+            note(f"norm_rope_mix_write_{mode}_{tag}",
+                 time_kernel(lambda: ops.norm_rope_mix_write(q, k, v, first, 0.3, q_out, pos, entry, table, pools[0], pools[1],
+                                                             page, rot, hd // 2, mode, wq, wk, 1e-6)), moved)
+        inv_full = torch.rand(hd // 2, dtype=torch.float64, device=dev)
+        note(f"rope_kv_write_{tag} (Llama)",
+             time_kernel(lambda: ops.rope_kv_write(q, k, v, pos, entry, table, pools[0], pools[1], page, inv_full, hd, None)),
+             tokens * (heads * hd * 2 * 2 + kv * hd * 2 * 4))
+        # the router, and the experts pair by pair (steps of few tokens)
+        h = torch.randn((tokens, width), device=dev).to(bf)
+        route_bytes = tokens * width * 2 + experts * width * 4
+        note(f"moe_route_sigmoid_two_best_{tag}",
+             time_kernel(lambda: ops.moe_route(h, router, correction, top, 4, 2, True, 2, False)), route_bytes)
+        note(f"moe_route_softmax_{tag} (Bunosun)",
+             time_kernel(lambda: ops.moe_route(h, router, correction, top, 4, 2)), route_bytes)
+        if tokens <= 8:
+            chosen, weights = ops.moe_route(h, router, correction, top, 4, 2, True, 2, False)
+            act = torch.empty((tokens * top, ff), dtype=bf, device=dev)
+            res = torch.empty((tokens, width), dtype=bf, device=dev)
+            note(f"moe_up_{tag}", time_kernel(lambda: ops.moe_up(h, up, chosen, act)), tokens * top * ff * width * 2)
+            note(f"moe_gate_up_{tag} (Bunosun)", time_kernel(lambda: ops.moe_gate_up(h, gate_up, chosen, act)),
+                 tokens * top * 2 * ff * width * 2)
+            note(f"moe_down_{tag} (both)", time_kernel(lambda: ops.moe_down(act, down, chosen, weights, None, res)),
+                 tokens * top * ff * width * 2)
+        z = torch.randn((tokens, 4 * width), device=dev).to(bf)
+        squared = torch.empty_like(z)
+        note(f"bias_act_relu2_{tag}", time_kernel(lambda: ops.bias_act(z, None, squared, "relu2")), tokens * 4 * width * 4)
+        half = torch.empty((tokens, 2 * width), dtype=bf, device=dev)
+        note(f"swiglu_{tag} (Llama)", time_kernel(lambda: ops.swiglu(z, half)), tokens * 4 * width * 3)
+    # attention of 64 single tokens over 2,048 keys (a window of 1,024, and none): the bias by distance and the
+    # gate per head beside the Llama layer's kernel at the same shape
+    keys, batch = 2048, 64
+    n_pages = batch * keys // page
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, keys // page)
+    pos = torch.full((batch,), keys - 1, dtype=torch.int32, device=dev)
+    ent = torch.arange(batch, dtype=torch.int32, device=dev)
+    q = torch.randn((batch, heads, hd), device=dev).to(bf)
+    res = torch.empty_like(q)
+    kvp = torch.randn((2, n_pages, kv, page, hd), device=dev).to(bf)
+    bias = bias_by_distance(torch.randn((32, heads), device=dev), 4096.0)
+    gate = torch.randn((batch, heads), device=dev).to(bf)
+    for window in (1024, None):
+        read = batch * (window or keys) * kv * hd * 2 * 2
+        name = f"w{window}" if window else "causal"
+        for splits in (1, 4):
+            scratch = torch.empty(ops.attention_decode_scratch_floats(batch, heads, hd, splits), device=dev)
+            note(f"attention_decode_bias_b64_{name}_splits{splits}",
+                 time_kernel(lambda: ops.attention_decode(q, kvp[0], kvp[1], table, pos, ent, res, page, window, 0.125, splits,
+                                                          scratch, extras=ops.attention_extras(q, None, None, True, 0.0, bias))),
+                 read)
+            note(f"attention_decode_gate_b64_{name}_splits{splits}",
+                 time_kernel(lambda: ops.attention_decode(q, kvp[0], kvp[1], table, pos, ent, res, page, window, 0.125, splits,
+                                                          scratch, extras=ops.attention_extras(q, None, gate, True))), read)
+            note(f"attention_decode_b64_{name}_splits{splits} (Llama)",
+                 time_kernel(lambda: ops.attention_decode(q, kvp[0], kvp[1], table, pos, ent, res, page, window, 0.125, splits,
+                                                          scratch)), read)
+    # a 2,048-token prompt through the tiled kernel, with and without the bias and the gate
+    tokens = 2048
+    n_pages = tokens // page
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, n_pages)
+    q = torch.randn((tokens, heads, hd), device=dev).to(bf)
+    res = torch.empty_like(q)
+    kvp = torch.randn((2, n_pages, kv, page, hd), device=dev).to(bf)
+    gate = torch.randn((tokens, heads), device=dev).to(bf)
+    rows = ops.attention_prefill_tile_rows()
+    tiles = torch.tensor([(r, min(rows, tokens - r), r, 0) for r in range(0, tokens, rows)], dtype=torch.int32, device=dev)
+    for window in (1024, None):
+        flops = 4.0 * heads * hd * sum(min(p + 1, window or tokens) for p in range(tokens))
+        name = f"w{window}" if window else "causal"
+        for what, ex in (("bias, split weights", ops.attention_extras(q, None, None, True, 0.0, bias)),
+                         ("gate, split weights", ops.attention_extras(q, None, gate, True)),
+                         ("split weights", ops.attention_extras(q, None, None, True)),
+                         ("plain, mma.sync", None)):
+            ms = time_kernel(lambda: ops.attention_prefill(q, kvp[0], kvp[1], table, tiles, res, page, window, 0.125, extras=ex))
+            note(f"attention_prefill_T2048_{name} ({what})", ms, None, flops)
+        if ops.attention_prefill_tcgen05_supports(q, kvp[0], page):
+            ms = time_kernel(lambda: ops.attention_prefill_tcgen05(q, kvp[0], kvp[1], table, tiles, res, page, window, 0.125,
+                                                                   None, 1, None, False))
+            note(f"attention_prefill_T2048_{name} (tcgen05: Llama)", ms, None, flops)
+    return out
+
+
 def run_design(args) -> dict:
     """Prefill and decode throughput of the named design at a few sizes beside the Llama
     decoder at the same width, depth and vocabulary (random weights), and the design's own
@@ -985,8 +1144,8 @@ def run_design(args) -> dict:
     prompt, batch, context = 2048, 8, 2048
     with ClockSampler() as clocks:
         for width, layers in ((1024, 6), (2048, 6), (4096, 3)):
-            mine = {"bunosun": bunosun_config, "rerilorn": rerilorn_config, "simetar": simetar_config}[args.design](
-                width, layers)
+            mine = {"bunosun": bunosun_config, "rerilorn": rerilorn_config, "simetar": simetar_config,
+                    "puvirax": puvirax_config}[args.design](width, layers)
             for name, cfg in ((args.design, mine), ("llama", llama_config_like(width, layers))):
                 vocab = cfg.get("vocab", cfg.get("vocab_size"))
                 n_pages = (batch * (context + 256) + 4 * prompt) // PAGE_SIZE
@@ -1018,8 +1177,8 @@ def run_design(args) -> dict:
                 del engine
                 gc.collect()
                 torch.cuda.empty_cache()
-        kernels = {"bunosun": bunosun_kernels, "rerilorn": design_kernels, "simetar": simetar_kernels}[args.design](
-            2048, pk)
+        kernels = {"bunosun": bunosun_kernels, "rerilorn": design_kernels, "simetar": simetar_kernels,
+                   "puvirax": puvirax_kernels}[args.design](2048, pk)
     summary = clocks.summary()
     return {"metric": f"prefill and decode tok/s of the {args.design.capitalize()} design beside the Llama decoder at "
                       f"equal sizes",
@@ -1033,8 +1192,8 @@ def run_design(args) -> dict:
 
 def main() -> int:
     p = argparse.ArgumentParser()
-    p.add_argument("--design", default="llama", choices=["llama", "rerilorn", "bunosun", "simetar"],
-                   help="llama: the headline workload (the default); rerilorn, bunosun, simetar: that design's prefill and "
+    p.add_argument("--design", default="llama", choices=["llama", "rerilorn", "bunosun", "simetar", "puvirax"],
+                   help="llama: the headline workload (the default); rerilorn, bunosun, simetar, puvirax: that design's prefill and "
                         "decode throughput at a few sizes beside the Llama decoder at equal sizes, and its kernels alone")
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=128)
@@ -1057,7 +1216,7 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     args.warmup = max(3, args.warmup)
-    if args.design in ("rerilorn", "bunosun", "simetar"):
+    if args.design in ("rerilorn", "bunosun", "simetar", "puvirax"):
         args.steps = min(args.steps, 64)
         print(json.dumps(run_design(args)))
         return 0

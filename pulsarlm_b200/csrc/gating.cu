@@ -3,6 +3,7 @@
 //
 //   gated_act:     out[t, i] = act(in[t, i]) * in[t, width + i]      act: silu or the tanh form of GELU
 //   sigmoid_gate:  x[t, i]  *= sigmoid(gate[t, i])
+//   sigmoid_gate_heads:  x[t, h, :] *= sigmoid(gate[t, h])     one gate per head
 //
 // Arithmetic in fp32 (expf, tanhf), one rounding on the store.
 #include "common.cuh"
@@ -87,6 +88,29 @@ __global__ void sigmoid_gate_quads_kernel(scalar_t* __restrict__ x, int64_t x_st
     }
 }
 
+// One gate per head: x [T, heads, row] times sigmoid(gate [T, heads]); PER elements a thread (1 or 4).
+template <typename scalar_t, int PER>
+__global__ void sigmoid_gate_heads_kernel(scalar_t* __restrict__ x, int64_t x_stride, const scalar_t* __restrict__ gate,
+                                          int64_t gate_stride, int64_t tokens, int heads, int row) {
+    pl_grid_trigger();
+    pl_grid_wait();
+    const int pieces = heads * row / PER;
+    const int64_t total = tokens * pieces;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t t = idx / pieces;
+        const int i = PER * static_cast<int>(idx - t * pieces);
+        const float factor = 1.0f / (1.0f + expf(-pl_load(gate + t * gate_stride + i / row)));
+        scalar_t* at = x + t * x_stride + i;
+        if (PER == 4) {
+            const float4 v = pl_load4(at);
+            pl_store4(at, make_float4(v.x * factor, v.y * factor, v.z * factor, v.w * factor));
+        } else {
+            pl_store(at, pl_load(at) * factor);
+        }
+    }
+}
+
 }  // namespace
 
 // in [T, 2 * width] (gate columns, then up columns), out [T, width], both dense, in the
@@ -142,5 +166,34 @@ PL_API int pl_sigmoid_gate(void* x, int64_t x_stride, const void* gate, int64_t 
                              n_tokens, width);
     });
     PL_CHECK_LAUNCH("sigmoid_gate");
+    return 0;
+}
+
+// x [T, n_heads, row] (x_stride elements between tokens) is multiplied in place by sigmoid(gate [T, n_heads])
+// (gate_stride between rows), one gate per head, both in the engine's dtype.
+PL_API int pl_sigmoid_gate_heads(void* x, int64_t x_stride, const void* gate, int64_t gate_stride, int n_tokens,
+                                 int n_heads, int row, int dtype, cudaStream_t stream) {
+    PL_REQUIRE(n_tokens >= 0 && n_heads > 0 && row > 0, "sigmoid_gate_heads: bad sizes tokens=%d heads=%d row=%d",
+               n_tokens, n_heads, row);
+    if (n_tokens == 0) {
+        return 0;
+    }
+    const int threads = 256;
+    const uintptr_t piece = dtype == PL_F32 ? 16 : 8;  // four elements
+    const bool quads = row % 4 == 0 && x_stride % 4 == 0 && reinterpret_cast<uintptr_t>(x) % piece == 0;
+    const int64_t total = static_cast<int64_t>(n_tokens) * n_heads * row / (quads ? 4 : 1);
+    const int blocks = static_cast<int>(std::min<int64_t>((total + threads - 1) / threads, 148 * 16));
+    PL_DISPATCH_DTYPE(dtype, "sigmoid_gate_heads", {
+        if (quads) {
+            pl_launch_overlapped(sigmoid_gate_heads_kernel<scalar_t, 4>, dim3(blocks), dim3(threads), 0, stream,
+                                 static_cast<scalar_t*>(x), x_stride, static_cast<const scalar_t*>(gate), gate_stride,
+                                 n_tokens, n_heads, row);
+        } else {
+            pl_launch_overlapped(sigmoid_gate_heads_kernel<scalar_t, 1>, dim3(blocks), dim3(threads), 0, stream,
+                                 static_cast<scalar_t*>(x), x_stride, static_cast<const scalar_t*>(gate), gate_stride,
+                                 n_tokens, n_heads, row);
+        }
+    });
+    PL_CHECK_LAUNCH("sigmoid_gate_heads");
     return 0;
 }

@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 26
+ABI_VERSION = 27
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -111,6 +111,7 @@ _SIGNATURES = {
     "pl_add_layernorm": [_PTR, _PTR, _PTR, _PTR, _F32, _PTR, _PTR, _PTR, _F32, _PTR, _I32, _I32, _I32, _I32, _PTR],
     "pl_gated_act": [_PTR, _PTR, _I32, _I32, _I32, _I32, _PTR],
     "pl_sigmoid_gate": [_PTR, _I64, _PTR, _I64, _I32, _I32, _I32, _PTR],
+    "pl_sigmoid_gate_heads": [_PTR, _I64, _PTR, _I64, _I32, _I32, _I32, _I32, _PTR],
     "pl_conv_norm_rope_write": [_PTR, _I64, _PTR, _PTR, _I32, _PTR, _PTR, _I32, _PTR, _PTR, _F32, _PTR, _I32, _I32, _F32,
                                 _PTR, _PTR, _PTR, _I32, _PTR, _I64, _PTR, _PTR, _I64, _I64, _I32, _I32, _I32, _I32, _I32,
                                 _I32, _I32, _PTR, _PTR],
@@ -738,6 +739,17 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
     assert gate.shape == x.shape and gate.dtype == x.dtype and x.stride(1) == 1 and gate.stride(1) == 1
     _call("pl_sigmoid_gate", _p(x), x.stride(0) if tokens > 1 else width, _p(gate),
           gate.stride(0) if tokens > 1 else width, tokens, width, _code(x.dtype), _stream())
+
+
+def sigmoid_gate_heads(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place; x [T, nh, row] (rows of a head dense, row stride free), gate
+    [T, nh] logits (row stride free)."""
+    _dev(x, gate)
+    tokens, n_heads, row = x.shape
+    assert gate.shape == (tokens, n_heads) and gate.dtype == x.dtype and gate.stride(1) == 1
+    assert x.stride(2) == 1 and x.stride(1) == row
+    _call("pl_sigmoid_gate_heads", _p(x), x.stride(0) if tokens > 1 else n_heads * row, _p(gate),
+          gate.stride(0) if tokens > 1 else n_heads, tokens, n_heads, row, _code(x.dtype), _stream())
 
 
 def conv_norm_rope_write(proj: torch.Tensor, bias: torch.Tensor | None, conv_weight: torch.Tensor | None,

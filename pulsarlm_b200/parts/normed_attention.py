@@ -71,8 +71,10 @@ class NormedAttention(Attention):
     norms, rotates, mixes and writes q and the cache rows as rows of a common size (the larger of
     dim and vdim, rounded up to a multiple of 16, zeros past a row's own columns), so that the
     paged attention kernels, which know one row size, run them unchanged; the o projection's
-    weights get zero columns to match, so nothing is compacted in between. Bias and gate travel
-    to the attention kernels as extras.
+    weights get zero columns to match, so nothing is compacted in between. A bias travels to the
+    attention kernels as an extra, and a gate with it; a layer whose only extra would be the gate
+    keeps the plain attention kernels in bfloat16 (tcgen05 for prompt portions at rows of 64 and
+    128, work lists for many single tokens) and multiplies by the gate in a small kernel afterwards.
 
     params: hidden_size, n_heads, n_kv_heads, head_dim (dim), value_dim, scale, window, norm_eps,
     qk_norm, position, bias_far, bias_rows (optional), value_mix, value_stream, head_gate."""
@@ -93,7 +95,8 @@ class NormedAttention(Attention):
             raise ValueError(f"normed_attention: unknown qk_norm {self.qk_norm!r} (known: {', '.join(QK_NORMS)})")
         self.norm_eps = float(p.get("norm_eps") or 0.0)
         self.bias_far = float(p["bias_far"]) if p.get("bias_far") is not None else None
-        self.head_gate = bool(p.get("head_gate", False))
+        self.gated = bool(p.get("head_gate", False))
+        self.head_gate = self.gated   # (whether the gate rides along inside the attention kernels: see bind_cache)
         self.value_mix = p.get("value_mix")
         self.value_stream = p.get("value_stream")
         if self.value_mix not in (None, "source", "mix") or (self.value_mix and not self.value_stream):
@@ -129,7 +132,7 @@ class NormedAttention(Attention):
         t = self.spec.tensors
         nh, vd, row = self.n_heads, self.value_dim, self.row
         stacked = [tensors[t["q"]], tensors[t["k"]], tensors[t["v"]]]
-        if self.head_gate:
+        if self.gated:
             stacked.append(tensors[t["gate"]])
         width = sum(w.shape[0] for w in stacked)
         if self.ctx.dtype == torch.bfloat16 and width % 8:
@@ -156,6 +159,14 @@ class NormedAttention(Attention):
     def cache_read_need(self) -> KVCacheNeed:
         return self.cache_need()
 
+    def bind_cache(self, binding) -> None:
+        super().bind_cache(binding)
+        # With the cache's page size known: a gate that would be the layer's only extra stays out of the attention
+        # kernels where the plain tensor-core kernels take the shape (they are the faster builds).
+        if self.gated and self.distance_bias is None and self.bias_far is None and self.ctx.dtype == torch.bfloat16:
+            self._decode_kernel = self._prefill_kernel = None
+            self.head_gate = not all(self._kernels(self.ctx.dtype))
+
     def _folds_rope(self, tokens, batch, inv_freq, rotary) -> bool:
         return False  # (norms, rotation and mixing are a kernel of their own)
 
@@ -172,7 +183,7 @@ class NormedAttention(Attention):
         q = proj[:, :q_end].view(tokens, nh, hd)
         k = proj[:, q_end:k_end].view(tokens, nkv, hd)
         v = proj[:, k_end:v_end].view(tokens, nkv, vd)
-        gate = proj[:, v_end:v_end + nh] if self.head_gate else None
+        gate = proj[:, v_end:v_end + nh] if self.gated else None
         first = None
         if self.value_mix == "source":
             batch.extras[("values", self.value_stream)] = v
@@ -186,5 +197,7 @@ class NormedAttention(Attention):
                                 cache.v_pool, cache.page_size, inv_freq, rotary, self.qk_norm, self.q_weight,
                                 self.k_weight, self.norm_eps, batch.status)
         out = torch.empty((tokens, nh, row), dtype=h.dtype, device=h.device)
-        self.attend(q_rows, out, table, batch, gate=gate)
+        self.attend(q_rows, out, table, batch, gate=gate if self.head_gate else None)
+        if self.gated and not self.head_gate:
+            ops.sigmoid_gate_heads(out, gate)
         return linear(out.view(tokens, nh * row), self.o)

@@ -141,6 +141,21 @@ def test_norms_rotation_and_value_mixing_on_the_way_to_the_cache(mode, heads, kv
             assert float(got_k[:, dim:].abs().sum()) == 0.0 and float(got_v[:, vdim:].abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("heads,row", [(4, 96), (3, 10), (32, 64)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gate_per_head_after_attention(heads, row, dtype):
+    """The gate of a layer whose attention runs on the plain kernels: one sigmoid per (token, head) over the head's
+    row, the logits read as columns of a wider matrix."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(row)
+    x = torch.randn(19, heads, row, generator=gen).to(dtype)
+    wide = torch.randn(19, heads + 5, generator=gen).to(dtype)
+    want = x.double() * torch.sigmoid(wide[:, 2: 2 + heads].double())[:, :, None]
+    got = x.to(DEV)
+    ops.sigmoid_gate_heads(got, wide.to(DEV)[:, 2: 2 + heads])
+    assert plain.relative_error_of(got.cpu(), want) < _bar(dtype)
+
+
 def _attention_case(gen, lengths, heads, kv, dim, page, dtype, rows, far, spike_at, queries):
     """Paged keys and values of some requests, a bias table, queries for chosen (request, position) pairs; a key at
     distance `spike_at` of every query lined up with head 0's query so that it dominates where it is in reach."""
