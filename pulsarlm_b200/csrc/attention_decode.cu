@@ -94,7 +94,7 @@ struct DecodeParams {
     int split_weights;
     float cap_log2;        // score cap * log2 e (0: none) and scale / cap
     float scale_over_cap;
-    const float* distance_bias;  // fp32 [bias_rows, n_heads] (nullptr: none), see PlAttentionExtras
+    const float* distance_bias;  // fp32 [n_heads, bias_rows] (nullptr: none), see PlAttentionExtras
     int bias_rows;
 };
 
@@ -343,7 +343,7 @@ __device__ __forceinline__ void attention_decode_share(const DecodeParams& p, un
                     // the bias of this head (row g, or g + 8, of the group) at the key's distance, in the exponent's units
                     const int hg = min(e < 2 ? g : g + 8, p.group - 1);
                     const int d = min(ctx - 1 - key, p.bias_rows - 1);
-                    scaled = fmaf(__ldg(p.distance_bias + static_cast<int64_t>(d) * p.n_heads + kv_head * p.group + hg),
+                    scaled = fmaf(__ldg(p.distance_bias + static_cast<int64_t>(kv_head * p.group + hg) * p.bias_rows + d),
                                   1.4426950408889634f, scaled);
                 }
                 s[j][e] = ok ? scaled : -INFINITY;

@@ -49,7 +49,7 @@ struct PrefillParams {
     int split_weights;
     float cap_log2;        // score cap * log2 e (0: none) and scale / cap
     float scale_over_cap;
-    const float* distance_bias;  // fp32 [bias_rows, n_heads] (nullptr: none), see PlAttentionExtras
+    const float* distance_bias;  // fp32 [n_heads, bias_rows] (nullptr: none), see PlAttentionExtras
     int bias_rows;
     int n_heads;
 };
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_kernel(const Pr
                 float x = pl_exponent_of_score(raw, p.scale_log2, p.cap_log2, p.scale_over_cap);
                 if (p.distance_bias != nullptr) {
                     const int d = min(max(pos - key, 0), p.bias_rows - 1);
-                    x = fmaf(__ldg(p.distance_bias + static_cast<int64_t>(d) * p.n_heads + head), 1.4426950408889634f, x);
+                    x = fmaf(__ldg(p.distance_bias + static_cast<int64_t>(head) * p.bias_rows + d), 1.4426950408889634f, x);
                 }
                 return x;
             };

@@ -136,7 +136,7 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
                     }
                     if (distance_bias != nullptr) {
                         // a learned bias by distance and head joins the scaled score (the scale does not touch it)
-                        s += distance_bias[static_cast<int64_t>(min(p - j, bias_rows - 1)) * n_heads + h];
+                        s += distance_bias[static_cast<int64_t>(h) * bias_rows + min(p - j, bias_rows - 1)];
                     }
                 } else if (status != nullptr) {
                     atomicOr(status, 4);
@@ -233,8 +233,8 @@ __global__ void attention_simt_kernel(const scalar_t* __restrict__ q, int64_t q_
 // score s becomes softcap * tanh(s / softcap) before the softmax (0: off). sinks (fp32
 // [n_heads], may be nullptr): exp(sinks[h]) is added to head h's softmax denominator. gate
 // ([T, n_heads] logits with gate_row_stride elements between rows, may be nullptr): head
-// h's output for token t is multiplied by sigmoid(gate[t, h]). distance_bias (fp32 [bias_rows,
-// n_heads], may be nullptr): distance_bias[min(pos - key's position, bias_rows - 1), h] is added
+// h's output for token t is multiplied by sigmoid(gate[t, h]). distance_bias (fp32 [n_heads,
+// bias_rows], may be nullptr): distance_bias[h, min(pos - key's position, bias_rows - 1)] is added
 // to head h's scaled score.
 PL_API int pl_attention_simt(const void* q, int64_t q_row_stride, const void* k_pool, const void* v_pool,
                              int64_t page_stride, int64_t head_stride, int page_size, int n_pages,

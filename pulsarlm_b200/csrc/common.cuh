@@ -158,9 +158,9 @@ __device__ __forceinline__ float pl_block_max(float v, float* scratch) {
 // sigmoid(gate[t, h]). split_weights != 0: the tensor-core kernels feed the softmax weights
 // to the value product as two bfloat16 terms (the rounded weight and what the rounding
 // lost), so the weights keep 16 mantissa bits instead of 8. softcap > 0: every scaled score s
-// becomes softcap * tanh(s / softcap) before the softmax. distance_bias: fp32 [bias_rows, n_heads];
-// distance_bias[min(d, bias_rows - 1), h] joins head h's scaled (and capped) score of a key d tokens
-// before the query; the scale does not touch it.
+// becomes softcap * tanh(s / softcap) before the softmax. distance_bias: fp32 [n_heads, bias_rows]
+// (a head's entries side by side); distance_bias[h, min(d, bias_rows - 1)] joins head h's scaled (and
+// capped) score of a key d tokens before the query; the scale does not touch it.
 struct PlAttentionExtras {
     const float* sinks;
     const void* gate;

@@ -163,6 +163,191 @@ norm_rope_mix_write_kernel(const scalar_t* __restrict__ q, const scalar_t* __res
     }
 }
 
+// Sixteen bytes of a row as floats.
+template <typename scalar_t>
+struct Piece;
+template <>
+struct Piece<float> {
+    static constexpr int kCount = 4;
+    __device__ static __forceinline__ void load(const float* p, float* out) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    }
+    __device__ static __forceinline__ void store(float* p, const float* in) {
+        *reinterpret_cast<float4*>(p) = make_float4(in[0], in[1], in[2], in[3]);
+    }
+};
+template <>
+struct Piece<__nv_bfloat16> {
+    static constexpr int kCount = 8;
+    __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* out) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            out[2 * i] = __uint_as_float(words[i] << 16);
+            out[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+        }
+    }
+    __device__ static __forceinline__ void store(__nv_bfloat16* p, const float* in) {
+        uint4 raw;
+        uint32_t* words = reinterpret_cast<uint32_t*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+            words[i] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+        *reinterpret_cast<uint4*>(p) = raw;
+    }
+};
+
+// The same for long steps: a block per token. The token's q | k | v columns (one stretch of the projection's
+// output) come into shared memory as floats in one pass of 16-byte loads, every thread's loads in flight at
+// once; the warps then work on their heads there and store whole 16-byte pieces. Every sum is added in the
+// order of the kernel above (a head by a warp, lanes striding its columns; a whole projection by the block's
+// 128 threads), so a token's bits do not depend on which of the two ran.
+template <typename scalar_t>
+__global__ void __launch_bounds__(kThreads)
+norm_rope_mix_write_row_kernel(const scalar_t* __restrict__ proj, int64_t row_stride,
+                               const scalar_t* __restrict__ v_first, int64_t v_first_stride, float lambda,
+                               scalar_t* __restrict__ q_out, const int32_t* __restrict__ pos,
+                               const int32_t* __restrict__ entry, const int32_t* __restrict__ table, int table_width,
+                               scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool, int64_t page_stride,
+                               int64_t head_stride, int page_size, int n_pages, const double* __restrict__ inv_freq,
+                               int rotary, int n_heads, int n_kv, int dim, int vdim, int row, int mode,
+                               const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                               int load_pieces, int store_pieces, int32_t* status) {
+    extern __shared__ float shared[];  // [rotary] cos | sin, [32] scratch, the token's columns
+    constexpr int kPer = Piece<scalar_t>::kCount;
+    pl_grid_trigger();
+    pl_grid_wait();
+    const int t = blockIdx.x;
+    const int p = pos[t];
+    const int half = rotary / 2;
+    float* cs = shared;
+    float* sn = shared + half;
+    float* scratch = shared + rotary;
+    float* cols = scratch + 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = kThreads / 32;
+    const int q_cols = n_heads * dim, k_cols = n_kv * dim, total = q_cols + k_cols + n_kv * vdim;
+    const scalar_t* src = proj + t * row_stride;
+    int done = 0;
+    if (load_pieces) {
+        done = total / kPer * kPer;
+        for (int i = threadIdx.x * kPer; i < done; i += kThreads * kPer) {
+            float piece[kPer];
+            Piece<scalar_t>::load(src + i, piece);
+#pragma unroll
+            for (int u = 0; u < kPer; ++u) {
+                cols[i + u] = piece[u];
+            }
+        }
+    }
+    for (int i = done + threadIdx.x; i < total; i += kThreads) {
+        cols[i] = pl_load(src + i);
+    }
+    if (inv_freq != nullptr) {
+        for (int j = threadIdx.x; j < half; j += kThreads) {
+            rope_sincos(p, inv_freq[j], cs[j], sn[j]);
+        }
+    }
+    int page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
+    if (page < 0 || page >= n_pages) {
+        if (threadIdx.x == 0 && status != nullptr) {
+            atomicOr(status, 2);
+        }
+        page = -1;
+    }
+    __syncthreads();
+    float whole_q = 1.0f, whole_k = 1.0f;
+    if (mode == kWhole) {
+        float sum = 0.0f;
+        for (int i = threadIdx.x; i < q_cols; i += kThreads) {
+            sum = fmaf(cols[i], cols[i], sum);
+        }
+        whole_q = rsqrtf(pl_block_sum(sum, scratch) / static_cast<float>(q_cols) + eps);
+        sum = 0.0f;
+        for (int i = threadIdx.x; i < k_cols; i += kThreads) {
+            sum = fmaf(cols[q_cols + i], cols[q_cols + i], sum);
+        }
+        whole_k = rsqrtf(pl_block_sum(sum, scratch) / static_cast<float>(k_cols) + eps);
+    }
+    const int n_slots = n_heads + 2 * n_kv;
+    for (int slot = warp; slot < n_slots; slot += warps) {
+        const bool is_v = slot >= n_heads + n_kv, is_q = slot < n_heads;
+        if (!is_q && page < 0) {
+            continue;
+        }
+        const int h = is_q ? slot : (is_v ? slot - n_heads - n_kv : slot - n_heads);
+        const int own = is_v ? vdim : dim;
+        float* buf = is_v ? cols + q_cols + k_cols + h * vdim : cols + slot * dim;
+        float after = 1.0f;
+        if (is_v) {
+            if (v_first != nullptr) {
+                const scalar_t* f = v_first + t * v_first_stride + static_cast<int64_t>(h) * vdim;
+                for (int d = lane; d < vdim; d += 32) {
+                    buf[d] = __fmaf_rn(lambda, pl_load(f + d), __fmul_rn(1.0f - lambda, buf[d]));
+                }
+            }
+        } else {
+            const float* weight = is_q ? q_weight : k_weight;
+            if (weight != nullptr && mode == kWhole) {
+                weight += static_cast<int64_t>(h) * dim;
+            }
+            float r = 1.0f;
+            if (mode == kPerHead) {
+                float sum = 0.0f;
+                for (int d = lane; d < dim; d += 32) {
+                    sum = fmaf(buf[d], buf[d], sum);
+                }
+                r = rsqrtf(pl_warp_sum(sum) / static_cast<float>(dim) + eps);
+            } else if (mode == kWhole) {
+                r = is_q ? whole_q : whole_k;
+            }
+            if (mode == kPerHead || mode == kWhole) {
+                for (int d = lane; d < dim; d += 32) {
+                    const float scaled = buf[d] * r;
+                    buf[d] = weight != nullptr ? scaled * weight[d] : scaled;
+                }
+            }
+            __syncwarp();
+            if (inv_freq != nullptr) {
+                for (int j = lane; j < half; j += 32) {
+                    const float lo = buf[j], hi = buf[j + half];
+                    buf[j] = rope_lo(lo, hi, cs[j], sn[j]);
+                    buf[j + half] = rope_hi(lo, hi, cs[j], sn[j]);
+                }
+                __syncwarp();
+            }
+            if (mode == kUnitAfter) {
+                float sum2 = 0.0f;
+                for (int d = lane; d < dim; d += 32) {
+                    sum2 = fmaf(buf[d], buf[d], sum2);
+                }
+                after = rsqrtf(pl_warp_sum(sum2) / static_cast<float>(dim) + eps);
+            }
+        }
+        __syncwarp();
+        scalar_t* to = is_q ? q_out + (static_cast<int64_t>(t) * n_heads + h) * row
+                            : (is_v ? v_pool : k_pool) + page * page_stride + h * head_stride +
+                                  static_cast<int64_t>(p % page_size) * row;
+        if (store_pieces) {
+            for (int d0 = lane * kPer; d0 < row; d0 += 32 * kPer) {
+                float piece[kPer];
+#pragma unroll
+                for (int u = 0; u < kPer; ++u) {
+                    piece[u] = d0 + u < own ? buf[d0 + u] * after : 0.0f;
+                }
+                Piece<scalar_t>::store(to + d0, piece);
+            }
+        } else {
+            for (int d = lane; d < row; d += 32) {
+                pl_store(to + d, d < own ? buf[d] * after : 0.0f);
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // q [T, n_heads, dim], k [T, n_kv, dim], v [T, n_kv, vdim] with `row_stride` elements between
@@ -192,7 +377,37 @@ PL_API int pl_norm_rope_mix_write(const void* q, const void* k, const void* v, i
         return 0;
     }
     const int n_slots = n_heads + 2 * n_kv;
-    const int heads_per_block = n_tokens >= 64 ? n_slots : 4;
+    // Long steps whose q, k and v are one stretch of the projection's output: a block per token that brings the
+    // stretch into shared memory first (16-byte loads and stores where the addresses allow).
+    const size_t elem = dtype == PL_F32 ? 4 : 2;
+    const int64_t q_cols = static_cast<int64_t>(n_heads) * dim, k_cols = static_cast<int64_t>(n_kv) * dim;
+    const size_t row_smem = (static_cast<size_t>(rotary) + 32 + q_cols + k_cols + static_cast<size_t>(n_kv) * vdim) * sizeof(float);
+    const bool one_stretch = static_cast<const char*>(k) == static_cast<const char*>(q) + q_cols * elem &&
+        static_cast<const char*>(v) == static_cast<const char*>(k) + k_cols * elem;
+    if (n_tokens >= 256 && one_stretch && row_smem <= 160 * 1024) {
+        const int per = static_cast<int>(16 / elem);
+        const auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+        const int load_pieces = aligned(q) && row_stride % per == 0;
+        const int store_pieces = row % per == 0 && aligned(q_out) && aligned(k_pool) && aligned(v_pool) &&
+            page_stride % per == 0 && head_stride % per == 0;
+        PL_DISPATCH_DTYPE(dtype, "norm_rope_mix_write", {
+            if (row_smem > 48 * 1024) {
+                cudaFuncSetAttribute(norm_rope_mix_write_row_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(row_smem));
+            }
+            pl_launch_overlapped(norm_rope_mix_write_row_kernel<scalar_t>, dim3(n_tokens), dim3(kThreads), row_smem, stream,
+                                 static_cast<const scalar_t*>(q), row_stride, static_cast<const scalar_t*>(v_first),
+                                 v_first_stride, lambda, static_cast<scalar_t*>(q_out), pos, entry, table, table_width,
+                                 static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool), page_stride, head_stride,
+                                 page_size, n_pages, inv_freq, rotary, n_heads, n_kv, dim, vdim, row, mode, q_weight,
+                                 k_weight, eps, load_pieces, store_pieces, status);
+        });
+        PL_CHECK_LAUNCH("norm_rope_mix_write");
+        return 0;
+    }
+    // Else a warp takes a head at a time: a block of four warps gets four head slots in steps of few tokens (many
+    // small blocks fill the device) and eight in long steps (two a warp).
+    const int heads_per_block = n_tokens >= 256 ? 8 : 4;
     const size_t smem = (static_cast<size_t>(rotary) + 32 + static_cast<size_t>(kThreads / 32) * dim) * sizeof(float);
     PL_REQUIRE(smem <= 48 * 1024, "norm_rope_mix_write: a key size of %d is too large", dim);
     const dim3 grid(n_tokens, (n_slots + heads_per_block - 1) / heads_per_block);

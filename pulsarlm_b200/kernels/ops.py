@@ -988,13 +988,13 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     softcap * tanh(s / softcap) before the softmax. sinks fp32 [nh]: exp(sinks[h]) joins head
     h's softmax denominator (a term with no key and no value). gate [T, nh] logits (row
     stride free): head h's output for token t is multiplied by sigmoid(gate[t, h]). distance_bias
-    fp32 [rows, nh]: row min(distance, rows - 1) of it is added to the scaled scores of a key
-    `distance` tokens before the query."""
+    fp32 [nh, rows]: entry min(distance, rows - 1) of a head's row is added to its scaled scores of a
+    key `distance` tokens before the query."""
     _dev(q, k_pool, v_pool, table, pos, entry, out, status, mass_sum, weight_sum, query_weights, sinks, gate,
          distance_bias)
     if distance_bias is not None:
         assert distance_bias.dtype == torch.float32 and distance_bias.dim() == 2 and distance_bias.is_contiguous()
-        assert distance_bias.shape[1] == q.shape[1] and distance_bias.shape[0] > 0
+        assert distance_bias.shape[0] == q.shape[1] and distance_bias.shape[1] > 0
     if sinks is not None:
         assert sinks.dtype == torch.float32 and sinks.shape == (q.shape[1],) and sinks.is_contiguous()
     if gate is not None:
@@ -1019,7 +1019,7 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
           n_heads, n_kv, head_dim, int(window or 0), float(scale), float(softcap or 0.0), _code(q.dtype),
           _p(mass_sum), _p(weight_sum), _p(query_weights), _p(sinks), _p(gate),
           gate.stride(0) if gate is not None else 0, _p(distance_bias),
-          distance_bias.shape[0] if distance_bias is not None else 0, _p(status), _stream())
+          distance_bias.shape[1] if distance_bias is not None else 0, _p(status), _stream())
 
 
 def attention_decode_supports(head_dim: int, group: int, page_size: int, dtype: torch.dtype) -> bool:
@@ -1118,22 +1118,22 @@ def attention_extras(q: torch.Tensor, sinks: torch.Tensor | None, gate: torch.Te
     PlAttentionExtras): sinks fp32 [nh] (exp(sinks[h]) joins head h's denominator), gate [T, nh]
     logits in q's dtype (outputs times their sigmoid), split_weights (softmax weights enter the
     value product as two bfloat16 terms), softcap (> 0: scaled scores pass through softcap *
-    tanh(s / softcap)), distance_bias fp32 [rows, nh] (row min(distance, rows - 1) joins the scaled
-    scores of a key `distance` tokens before the query). None when nothing is asked for. The tensors
+    tanh(s / softcap)), distance_bias fp32 [nh, rows] (entry min(distance, rows - 1) of a head's row joins
+    its scaled scores of a key `distance` tokens before the query). None when nothing is asked for. The tensors
     must outlive the call that takes the struct."""
     if sinks is None and gate is None and not split_weights and not softcap and distance_bias is None:
         return None
     _dev(sinks, gate, distance_bias)
     if distance_bias is not None:
         assert distance_bias.dtype == torch.float32 and distance_bias.dim() == 2 and distance_bias.is_contiguous()
-        assert distance_bias.shape[1] == q.shape[1] and distance_bias.shape[0] > 0
+        assert distance_bias.shape[0] == q.shape[1] and distance_bias.shape[1] > 0
     if sinks is not None:
         assert sinks.dtype == torch.float32 and sinks.shape == (q.shape[1],) and sinks.is_contiguous()
     if gate is not None:
         assert gate.dtype == q.dtype and gate.shape == (q.shape[0], q.shape[1]) and gate.stride(1) == 1
     return _AttentionExtras(_p(sinks), _p(gate), gate.stride(0) if gate is not None else 0, int(bool(split_weights)),
                             float(softcap or 0.0), _p(distance_bias),
-                            distance_bias.shape[0] if distance_bias is not None else 0)
+                            distance_bias.shape[1] if distance_bias is not None else 0)
 
 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor,

@@ -31,7 +31,9 @@ def describe_puvirax(cfg: PuviraxConfig) -> ModelSpec:
         names = {"q": m + "q", "k": m + "k", "v": m + "v", "o": m + "o"}
         params = {"hidden_size": width, "n_heads": layer.heads, "n_kv_heads": layer.kv_heads, "head_dim": layer.dim,
                   "value_dim": layer.value_dim, "scale": layer.scale, "window": layer.window, "norm_eps": cfg.norm_eps,
-                  "position": PartSpec("none")}
+                  # (softmax weights enter the value product rounded once, as in the plain kernels: measured on this
+                  # design, the second bfloat16 term changes the logits' error by less than the runs differ)
+                  "split_weights": False, "position": PartSpec("none")}
         if layer.type == "attention":
             params["qk_norm"] = "unit_after"
             params["head_gate"] = True

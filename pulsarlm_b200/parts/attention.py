@@ -214,7 +214,8 @@ class Attention(Part):
     squashes scores), sink_logit (optional number s: one more term exp(s) joins every
     head's softmax denominator, with no key and no value), qk_norm_eps (with the q_norm /
     k_norm tensors: eps of the per-head RMS norm applied to q and k before the position
-    encoding).
+    encoding), split_weights (optional, default true: a layer with a cap, a sink, a bias or a gate
+    feeds its softmax weights to the value product in two bfloat16 terms; false: in one).
     tensors: q [nh*hd, H], k and v [nkv*hd, H], o [H, nh*hd]; optional q_norm and
     k_norm [hd] (kept in float32). q, k and v are stacked into one operand at load.
     """
@@ -238,10 +239,13 @@ class Attention(Part):
                       if self.sink_logit is not None else None)
         self.q_norm: torch.Tensor | None = None
         self.k_norm: torch.Tensor | None = None
-        # fp32 [rows, n_heads], set by a mixer that has one: row min(distance, rows - 1) joins the scaled
-        # scores of a key `distance` tokens before the query
+        # fp32 [n_heads, rows], set by a mixer that has one: entry min(distance, rows - 1) of a head's row joins
+        # its scaled scores of a key `distance` tokens before the query
         self.distance_bias: torch.Tensor | None = None
         self.head_gate = False  # (a mixer that multiplies every head's output by a sigmoid hands `attend` the logits)
+        # Whether the tensor-core kernels' build with extras feeds the softmax weights to the value product as two
+        # bfloat16 terms (16 mantissa bits) or as one (8, as the plain build does; a third less tensor-core work).
+        self.split_weights = bool(p.get("split_weights", True))
         self.position = build_part("position", self.param("position"), ctx)
         self.qkv: torch.Tensor | None = None
         self.o: torch.Tensor | None = None
@@ -566,8 +570,8 @@ class Attention(Part):
                                  batch.entry[:n_decode], out[:n_decode], cache.page_size, self.window, self.scale,
                                  splits, scratch, batch.status,
                                  extras=ops.attention_extras(q[:n_decode], self.sinks,
-                                                             gate[:n_decode] if gate is not None else None, True,
-                                                             self.softcap, bias))
+                                                             gate[:n_decode] if gate is not None else None,
+                                                             self.split_weights, self.softcap, bias))
         if n_decode == tokens:
             return
         tiles = plan.get("tiles")
@@ -575,7 +579,8 @@ class Attention(Part):
             # (the tile list covers exactly the tokens after the leading single tokens)
             ops.attention_prefill(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size, self.window,
                                   self.scale, batch.status,
-                                  extras=ops.attention_extras(q, self.sinks, gate, True, self.softcap, bias))
+                                  extras=ops.attention_extras(q, self.sinks, gate, self.split_weights, self.softcap,
+                                                              bias))
             return
         ops.attention_simt(q[n_decode:], cache.k_pool, cache.v_pool, table, batch.pos[n_decode:],
                            batch.entry[n_decode:], out[n_decode:], cache.page_size, self.window, self.scale,

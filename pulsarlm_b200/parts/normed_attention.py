@@ -33,9 +33,10 @@ def distance_bucket(distance: int, rows: int, far: float) -> int:
 
 
 def bias_by_distance(table: torch.Tensor, far: float) -> torch.Tensor:
-    """table [rows, heads] -> fp32 [D, heads] with row d = table[bucket(d)] for every distance up
-    to the first that lands in the last row; greater distances read the last row (the kernels
-    clamp the distance to D - 1)."""
+    """table [rows, heads] -> fp32 [heads, D] with column d = table[bucket(d)] for every distance up
+    to the first that lands in the last row; greater distances read the last column (the kernels
+    clamp the distance to D - 1). A head's entries lie side by side: the keys of a tile are
+    neighbours in distance."""
     rows = table.shape[0]
     picks = []
     d = 0
@@ -46,7 +47,7 @@ def bias_by_distance(table: torch.Tensor, far: float) -> torch.Tensor:
             break
         d += 1
     index = torch.tensor(picks, dtype=torch.long, device=table.device)
-    return table.float()[index].contiguous()
+    return table.float()[index].t().contiguous()
 
 
 @register_part("mixer", "normed_attention")

@@ -67,7 +67,8 @@ def test_bias_table_by_distance(rows, far):
     distance is its own row; the rows never go back; every later distance reads the last row."""
     table = torch.arange(rows * 3, dtype=torch.float32).view(rows, 3)
     by_distance = bias_by_distance(table, far)
-    picks = [int(r[0]) // 3 for r in by_distance]
+    assert by_distance.shape[0] == 3
+    picks = [int(value) // 3 for value in by_distance[0]]
     assert picks[: rows // 2] == list(range(rows // 2)) and picks[-1] == rows - 1 and picks == sorted(picks)
     assert picks == [plain.distance_bucket(d, rows, far) for d in range(len(picks))]
     for d in (len(picks), int(far), int(far) + 1, 10 * int(far)):

@@ -95,10 +95,10 @@ def test_norms_rotation_and_value_mixing_on_the_way_to_the_cache(mode, heads, kv
     row = -(-max(dim, vdim) // 16) * 16
     rot = {"base": 100.0, "dims": rotary, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 32}}
     inv_freq = plain.banded_frequencies(rot).to(DEV) if rotary else None
-    for lengths, starts in (([5, 3], [9, 0]), ([70, 33], [3, 20])):
+    for lengths, starts, spare in (([5, 3], [9, 0], 3), ([70, 33], [3, 20], 3), ([300, 40], [7, 0], 8), ([260], [0], 5)):
         tokens = sum(lengths)
         width = heads * dim + kv * dim + kv * vdim
-        proj = (torch.randn(tokens, width + 3, generator=gen) * 2).to(dtype)
+        proj = (torch.randn(tokens, width + spare, generator=gen) * 2).to(dtype)
         q = proj[:, : heads * dim].view(tokens, heads, dim)
         k = proj[:, heads * dim: (heads + kv) * dim].view(tokens, kv, dim)
         v = proj[:, (heads + kv) * dim: width].view(tokens, kv, vdim)
@@ -119,26 +119,41 @@ def test_norms_rotation_and_value_mixing_on_the_way_to_the_cache(mode, heads, kv
             qd, kd = plain.rms(qd, eps), plain.rms(kd, eps)
         vd = plain.mixed_values(v.double(), first.double() if mix else None, lam)
         n_pages, table = _paged([s + n for s, n in zip(starts, lengths)], page, gen)
-        k_pool = torch.full((n_pages, kv, page, row), 7.0, dtype=dtype, device=DEV)
-        v_pool = torch.full_like(k_pool, 7.0)
-        q_out = torch.full((tokens, heads, row), 7.0, dtype=dtype, device=DEV)
         dev = proj.to(DEV)
-        ops.norm_rope_mix_write(dev[:, : heads * dim].view(tokens, heads, dim),
-                                dev[:, heads * dim: (heads + kv) * dim].view(tokens, kv, dim),
-                                dev[:, (heads + kv) * dim: width].view(tokens, kv, vdim),
-                                first.to(DEV) if mix else None, lam, q_out, pos.int().to(DEV), entry.int().to(DEV),
-                                table.to(DEV), k_pool, v_pool, page, inv_freq, rotary, mode,
-                                wq.to(DEV) if mode in ("per_head", "whole") else None,
-                                wk.to(DEV) if mode in ("per_head", "whole") else None, eps)
+        weights = (wq.to(DEV), wk.to(DEV)) if mode in ("per_head", "whole") else (None, None)
+
+        def run(lo, hi):
+            """Tokens [lo, hi) of the step as a launch of their own, into fresh pools."""
+            k_pool = torch.full((n_pages, kv, page, row), 7.0, dtype=dtype, device=DEV)
+            v_pool = torch.full_like(k_pool, 7.0)
+            q_out = torch.full((hi - lo, heads, row), 7.0, dtype=dtype, device=DEV)
+            part = dev[lo:hi]
+            ops.norm_rope_mix_write(part[:, : heads * dim].view(hi - lo, heads, dim),
+                                    part[:, heads * dim: (heads + kv) * dim].view(hi - lo, kv, dim),
+                                    part[:, (heads + kv) * dim: width].view(hi - lo, kv, vdim),
+                                    first.to(DEV)[lo:hi] if mix else None, lam, q_out, pos[lo:hi].int().to(DEV),
+                                    entry[lo:hi].int().to(DEV), table.to(DEV), k_pool, v_pool, page, inv_freq, rotary, mode,
+                                    weights[0], weights[1], eps)
+            return q_out, k_pool, v_pool
+
+        q_out, k_pool, v_pool = run(0, tokens)
         bar = _bar(dtype)
         assert plain.relative_error_of(q_out[:, :, :dim].cpu(), qd) < bar
-        assert float(q_out[:, :, dim:].abs().max()) == 0.0 if row > dim else True
+        assert row == dim or float(q_out[:, :, dim:].abs().max()) == 0.0
         for t in range(tokens):
             p, e = int(pos[t]), int(entry[t])
             got_k = k_pool[table[e, p // page], :, p % page].cpu()
             got_v = v_pool[table[e, p // page], :, p % page].cpu()
             assert plain.relative_error_of(got_k[:, :dim], kd[t]) < bar and plain.relative_error_of(got_v[:, :vdim], vd[t]) < bar
             assert float(got_k[:, dim:].abs().sum()) == 0.0 and float(got_v[:, vdim:].abs().sum()) == 0.0
+        if tokens >= 256:
+            # a long step takes another kernel than a short one: the same bits all the same
+            q_short, k_short, v_short = run(10, 60)
+            assert torch.equal(q_short, q_out[10:60])
+            for t in range(10, 60):
+                p, e = int(pos[t]), int(entry[t])
+                at = (table[e, p // page], slice(None), p % page)
+                assert torch.equal(k_short[at], k_pool[at]) and torch.equal(v_short[at], v_pool[at])
 
 
 @pytest.mark.parametrize("heads,row", [(4, 96), (3, 10), (32, 64)])
