@@ -14,9 +14,11 @@
 //   columns, so that the paged attention kernels (one row size for q, k and v) run them as
 //   they are: a product with a zero adds nothing.
 //
-// Statistics, norm products, rotation and the mix are fp32, one rounding on each store. A
-// block has 128 threads whatever the step, a head is summed by one warp and a whole projection
-// by the block, so a token's sums are added in an order that only the sizes decide.
+// Statistics, norm products, rotation and the mix are fp32, one rounding on each store. Two
+// kernels: one that keeps a head's row in the registers of a group of lanes, eight columns a lane
+// (sizes in multiples of eight on 16-byte addresses: the usual case), and one that walks a head
+// column by column for every other shape. Which of them runs, and the order in which either adds
+// up a token's sums, depends on the sizes alone, never on the step.
 #include "rope_helpers.cuh"
 
 namespace {
@@ -168,7 +170,6 @@ template <typename scalar_t>
 struct Piece;
 template <>
 struct Piece<float> {
-    static constexpr int kCount = 4;
     __device__ static __forceinline__ void load(const float* p, float* out) {
         const float4 v = *reinterpret_cast<const float4*>(p);
         out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
@@ -179,7 +180,6 @@ struct Piece<float> {
 };
 template <>
 struct Piece<__nv_bfloat16> {
-    static constexpr int kCount = 8;
     __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* out) {
         const uint4 raw = *reinterpret_cast<const uint4*>(p);
         const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -201,24 +201,29 @@ struct Piece<__nv_bfloat16> {
     }
 };
 
-// The same for long steps: a block per token. The token's q | k | v columns (one stretch of the projection's
-// output) come into shared memory as floats in one pass of 16-byte loads, every thread's loads in flight at
-// once; the warps then work on their heads there and store whole 16-byte pieces. Every sum is added in the
-// order of the kernel above (a head by a warp, lanes striding its columns; a whole projection by the block's
-// 128 threads), so a token's bits do not depend on which of the two ran.
+// The same with sixteen bytes (bfloat16) or thirty-two (float32) a lane: eight columns. A head's row of the
+// common size is shared out over a group of `lanes` neighbouring lanes (a power of two, at least row / 8), so a
+// warp works on 32 / lanes heads at once, everything in registers: sums of squares inside the group by
+// shuffles, the rotation's partner columns (rotary / 2 columns away: a whole number of lanes) by a shuffle a
+// column. Every lane runs the same shuffles whatever its head is (a query, a key or a value head). Takes key,
+// value and row sizes and half the rotary width that are multiples of 8. The sums' order depends on the sizes
+// alone: a lane's eight columns in turn, then the group's lanes as a tree; a whole projection by the block's
+// 128 threads, eight columns a thread and turn, then the block's tree.
 template <typename scalar_t>
 __global__ void __launch_bounds__(kThreads)
-norm_rope_mix_write_row_kernel(const scalar_t* __restrict__ proj, int64_t row_stride,
-                               const scalar_t* __restrict__ v_first, int64_t v_first_stride, float lambda,
-                               scalar_t* __restrict__ q_out, const int32_t* __restrict__ pos,
-                               const int32_t* __restrict__ entry, const int32_t* __restrict__ table, int table_width,
-                               scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool, int64_t page_stride,
-                               int64_t head_stride, int page_size, int n_pages, const double* __restrict__ inv_freq,
-                               int rotary, int n_heads, int n_kv, int dim, int vdim, int row, int mode,
-                               const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
-                               int load_pieces, int store_pieces, int32_t* status) {
-    extern __shared__ float shared[];  // [rotary] cos | sin, [32] scratch, the token's columns
-    constexpr int kPer = Piece<scalar_t>::kCount;
+norm_rope_mix_write_pieces_kernel(const scalar_t* __restrict__ q, const scalar_t* __restrict__ k,
+                                  const scalar_t* __restrict__ v, int64_t row_stride,
+                                  const scalar_t* __restrict__ v_first, int64_t v_first_stride, float lambda,
+                                  scalar_t* __restrict__ q_out, const int32_t* __restrict__ pos,
+                                  const int32_t* __restrict__ entry, const int32_t* __restrict__ table,
+                                  int table_width, scalar_t* __restrict__ k_pool, scalar_t* __restrict__ v_pool,
+                                  int64_t page_stride, int64_t head_stride, int page_size, int n_pages,
+                                  const double* __restrict__ inv_freq, int rotary, int n_heads, int n_kv, int dim,
+                                  int vdim, int row, int heads_per_block, int lanes, int mode,
+                                  const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                                  int32_t* status) {
+    extern __shared__ float shared[];  // [rotary] cos | sin, [32] scratch
+    constexpr int kCols = 8;
     pl_grid_trigger();
     pl_grid_wait();
     const int t = blockIdx.x;
@@ -227,123 +232,159 @@ norm_rope_mix_write_row_kernel(const scalar_t* __restrict__ proj, int64_t row_st
     float* cs = shared;
     float* sn = shared + half;
     float* scratch = shared + rotary;
-    float* cols = scratch + 32;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = kThreads / 32;
-    const int q_cols = n_heads * dim, k_cols = n_kv * dim, total = q_cols + k_cols + n_kv * vdim;
-    const scalar_t* src = proj + t * row_stride;
-    int done = 0;
-    if (load_pieces) {
-        done = total / kPer * kPer;
-        for (int i = threadIdx.x * kPer; i < done; i += kThreads * kPer) {
-            float piece[kPer];
-            Piece<scalar_t>::load(src + i, piece);
-#pragma unroll
-            for (int u = 0; u < kPer; ++u) {
-                cols[i + u] = piece[u];
-            }
-        }
-    }
-    for (int i = done + threadIdx.x; i < total; i += kThreads) {
-        cols[i] = pl_load(src + i);
-    }
     if (inv_freq != nullptr) {
         for (int j = threadIdx.x; j < half; j += kThreads) {
             rope_sincos(p, inv_freq[j], cs[j], sn[j]);
         }
     }
-    int page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
-    if (page < 0 || page >= n_pages) {
-        if (threadIdx.x == 0 && status != nullptr) {
-            atomicOr(status, 2);
+    const int n_slots = n_heads + 2 * n_kv;
+    const int slot0 = blockIdx.y * heads_per_block;
+    const int slot1 = min(slot0 + heads_per_block, n_slots);
+    int page = -1;
+    if (slot1 > n_heads) {
+        page = table[static_cast<int64_t>(entry[t]) * table_width + p / page_size];
+        if (page < 0 || page >= n_pages) {
+            if (threadIdx.x == 0 && status != nullptr) {
+                atomicOr(status, 2);
+            }
+            page = -1;
         }
-        page = -1;
     }
-    __syncthreads();
+    auto load8 = [](const scalar_t* from, float* x) {
+        if constexpr (sizeof(scalar_t) == 2) {
+            Piece<scalar_t>::load(from, x);
+        } else {
+            Piece<scalar_t>::load(from, x);
+            Piece<scalar_t>::load(from + 4, x + 4);
+        }
+    };
+    auto store8 = [](scalar_t* to, const float* x) {
+        if constexpr (sizeof(scalar_t) == 2) {
+            Piece<scalar_t>::store(to, x);
+        } else {
+            Piece<scalar_t>::store(to, x);
+            Piece<scalar_t>::store(to + 4, x + 4);
+        }
+    };
     float whole_q = 1.0f, whole_k = 1.0f;
     if (mode == kWhole) {
-        float sum = 0.0f;
-        for (int i = threadIdx.x; i < q_cols; i += kThreads) {
-            sum = fmaf(cols[i], cols[i], sum);
+        // (uniform over the block: both conditions depend on the block's slots only)
+        if (slot0 < n_heads) {
+            float sum = 0.0f;
+            for (int i = threadIdx.x * kCols; i < n_heads * dim; i += kThreads * kCols) {
+                float x[kCols];
+                load8(q + t * row_stride + i, x);
+#pragma unroll
+                for (int u = 0; u < kCols; ++u) {
+                    sum = fmaf(x[u], x[u], sum);
+                }
+            }
+            whole_q = rsqrtf(pl_block_sum(sum, scratch) / static_cast<float>(n_heads * dim) + eps);
         }
-        whole_q = rsqrtf(pl_block_sum(sum, scratch) / static_cast<float>(q_cols) + eps);
-        sum = 0.0f;
-        for (int i = threadIdx.x; i < k_cols; i += kThreads) {
-            sum = fmaf(cols[q_cols + i], cols[q_cols + i], sum);
+        if (slot1 > n_heads && slot0 < n_heads + n_kv) {
+            float sum = 0.0f;
+            for (int i = threadIdx.x * kCols; i < n_kv * dim; i += kThreads * kCols) {
+                float x[kCols];
+                load8(k + t * row_stride + i, x);
+#pragma unroll
+                for (int u = 0; u < kCols; ++u) {
+                    sum = fmaf(x[u], x[u], sum);
+                }
+            }
+            whole_k = rsqrtf(pl_block_sum(sum, scratch) / static_cast<float>(n_kv * dim) + eps);
         }
-        whole_k = rsqrtf(pl_block_sum(sum, scratch) / static_cast<float>(k_cols) + eps);
     }
-    const int n_slots = n_heads + 2 * n_kv;
-    for (int slot = warp; slot < n_slots; slot += warps) {
-        const bool is_v = slot >= n_heads + n_kv, is_q = slot < n_heads;
-        if (!is_q && page < 0) {
-            continue;
-        }
+    __syncthreads();
+
+    const int groups = kThreads / lanes;
+    const int group = threadIdx.x / lanes, li = threadIdx.x % lanes, lane = threadIdx.x & 31;
+    const int e0 = li * kCols;
+    const int shift = half / kCols;  // lanes between a column and its partner in the rotation
+    for (int first = slot0; first < slot1; first += groups) {  // (every thread of the block makes every turn)
+        const int slot = first + group;
+        const bool valid = slot < slot1;
+        const bool is_q = slot < n_heads, is_v = slot >= n_heads + n_kv;
         const int h = is_q ? slot : (is_v ? slot - n_heads - n_kv : slot - n_heads);
         const int own = is_v ? vdim : dim;
-        float* buf = is_v ? cols + q_cols + k_cols + h * vdim : cols + slot * dim;
-        float after = 1.0f;
-        if (is_v) {
-            if (v_first != nullptr) {
-                const scalar_t* f = v_first + t * v_first_stride + static_cast<int64_t>(h) * vdim;
-                for (int d = lane; d < vdim; d += 32) {
-                    buf[d] = __fmaf_rn(lambda, pl_load(f + d), __fmul_rn(1.0f - lambda, buf[d]));
+        const bool mine = valid && e0 < own && (is_q || page >= 0);
+        float x[kCols];
+#pragma unroll
+        for (int u = 0; u < kCols; ++u) {
+            x[u] = 0.0f;
+        }
+        if (mine) {
+            load8((is_q ? q : (is_v ? v : k)) + t * row_stride + static_cast<int64_t>(h) * own + e0, x);
+            if (is_v && v_first != nullptr) {
+                float f[kCols];
+                load8(v_first + t * v_first_stride + static_cast<int64_t>(h) * vdim + e0, f);
+#pragma unroll
+                for (int u = 0; u < kCols; ++u) {
+                    x[u] = __fmaf_rn(lambda, f[u], __fmul_rn(1.0f - lambda, x[u]));
                 }
-            }
-        } else {
-            const float* weight = is_q ? q_weight : k_weight;
-            if (weight != nullptr && mode == kWhole) {
-                weight += static_cast<int64_t>(h) * dim;
-            }
-            float r = 1.0f;
-            if (mode == kPerHead) {
-                float sum = 0.0f;
-                for (int d = lane; d < dim; d += 32) {
-                    sum = fmaf(buf[d], buf[d], sum);
-                }
-                r = rsqrtf(pl_warp_sum(sum) / static_cast<float>(dim) + eps);
-            } else if (mode == kWhole) {
-                r = is_q ? whole_q : whole_k;
-            }
-            if (mode == kPerHead || mode == kWhole) {
-                for (int d = lane; d < dim; d += 32) {
-                    const float scaled = buf[d] * r;
-                    buf[d] = weight != nullptr ? scaled * weight[d] : scaled;
-                }
-            }
-            __syncwarp();
-            if (inv_freq != nullptr) {
-                for (int j = lane; j < half; j += 32) {
-                    const float lo = buf[j], hi = buf[j + half];
-                    buf[j] = rope_lo(lo, hi, cs[j], sn[j]);
-                    buf[j + half] = rope_hi(lo, hi, cs[j], sn[j]);
-                }
-                __syncwarp();
-            }
-            if (mode == kUnitAfter) {
-                float sum2 = 0.0f;
-                for (int d = lane; d < dim; d += 32) {
-                    sum2 = fmaf(buf[d], buf[d], sum2);
-                }
-                after = rsqrtf(pl_warp_sum(sum2) / static_cast<float>(dim) + eps);
             }
         }
-        __syncwarp();
-        scalar_t* to = is_q ? q_out + (static_cast<int64_t>(t) * n_heads + h) * row
-                            : (is_v ? v_pool : k_pool) + page * page_stride + h * head_stride +
-                                  static_cast<int64_t>(p % page_size) * row;
-        if (store_pieces) {
-            for (int d0 = lane * kPer; d0 < row; d0 += 32 * kPer) {
-                float piece[kPer];
+        const bool normed = mine && !is_v;
+        if (mode == kPerHead) {
+            float sum = 0.0f;
 #pragma unroll
-                for (int u = 0; u < kPer; ++u) {
-                    piece[u] = d0 + u < own ? buf[d0 + u] * after : 0.0f;
+            for (int u = 0; u < kCols; ++u) {
+                sum = fmaf(x[u], x[u], sum);
+            }
+            for (int offset = lanes / 2; offset > 0; offset >>= 1) {
+                sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+            }
+            if (normed) {
+                const float r = rsqrtf(sum / static_cast<float>(dim) + eps);
+                const float* weight = is_q ? q_weight : k_weight;
+#pragma unroll
+                for (int u = 0; u < kCols; ++u) {
+                    const float scaled = x[u] * r;
+                    x[u] = weight != nullptr ? scaled * weight[e0 + u] : scaled;
                 }
-                Piece<scalar_t>::store(to + d0, piece);
             }
-        } else {
-            for (int d = lane; d < row; d += 32) {
-                pl_store(to + d, d < own ? buf[d] * after : 0.0f);
+        } else if (mode == kWhole && normed) {
+            const float r = is_q ? whole_q : whole_k;
+            const float* weight = is_q ? q_weight : k_weight;
+#pragma unroll
+            for (int u = 0; u < kCols; ++u) {
+                const float scaled = x[u] * r;
+                x[u] = weight != nullptr ? scaled * weight[static_cast<int64_t>(h) * dim + e0 + u] : scaled;
             }
+        }
+        if (inv_freq != nullptr) {
+            const bool low = e0 < half, turns = normed && e0 < rotary;
+            const int partner = turns ? (low ? lane + shift : lane - shift) : lane;
+#pragma unroll
+            for (int u = 0; u < kCols; ++u) {
+                const float other = __shfl_sync(0xffffffffu, x[u], partner);
+                if (turns) {
+                    const int j = (low ? e0 : e0 - half) + u;
+                    x[u] = low ? rope_lo(x[u], other, cs[j], sn[j]) : rope_hi(other, x[u], cs[j], sn[j]);
+                }
+            }
+        }
+        if (mode == kUnitAfter) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int u = 0; u < kCols; ++u) {
+                sum = fmaf(x[u], x[u], sum);
+            }
+            for (int offset = lanes / 2; offset > 0; offset >>= 1) {
+                sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+            }
+            if (normed) {
+                const float after = rsqrtf(sum / static_cast<float>(dim) + eps);
+#pragma unroll
+                for (int u = 0; u < kCols; ++u) {
+                    x[u] *= after;
+                }
+            }
+        }
+        if (valid && e0 < row && (is_q || page >= 0)) {  // (columns past the head's own are zeros)
+            scalar_t* to = is_q ? q_out + (static_cast<int64_t>(t) * n_heads + h) * row
+                                : (is_v ? v_pool : k_pool) + page * page_stride + h * head_stride +
+                                      static_cast<int64_t>(p % page_size) * row;
+            store8(to + e0, x);
         }
     }
 }
@@ -377,36 +418,39 @@ PL_API int pl_norm_rope_mix_write(const void* q, const void* k, const void* v, i
         return 0;
     }
     const int n_slots = n_heads + 2 * n_kv;
-    // Long steps whose q, k and v are one stretch of the projection's output: a block per token that brings the
-    // stretch into shared memory first (16-byte loads and stores where the addresses allow).
+    // Sizes in whole pieces of eight columns, on 16-byte addresses: the kernel that keeps a head in registers.
     const size_t elem = dtype == PL_F32 ? 4 : 2;
-    const int64_t q_cols = static_cast<int64_t>(n_heads) * dim, k_cols = static_cast<int64_t>(n_kv) * dim;
-    const size_t row_smem = (static_cast<size_t>(rotary) + 32 + q_cols + k_cols + static_cast<size_t>(n_kv) * vdim) * sizeof(float);
-    const bool one_stretch = static_cast<const char*>(k) == static_cast<const char*>(q) + q_cols * elem &&
-        static_cast<const char*>(v) == static_cast<const char*>(k) + k_cols * elem;
-    if (n_tokens >= 256 && one_stretch && row_smem <= 160 * 1024) {
-        const int per = static_cast<int>(16 / elem);
-        const auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
-        const int load_pieces = aligned(q) && row_stride % per == 0;
-        const int store_pieces = row % per == 0 && aligned(q_out) && aligned(k_pool) && aligned(v_pool) &&
-            page_stride % per == 0 && head_stride % per == 0;
+    const auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    const int64_t step = static_cast<int64_t>(16 / elem);  // elements between addresses 16 bytes apart
+    const bool pieces = dim % 8 == 0 && vdim % 8 == 0 && row % 8 == 0 && row <= 256 && (rotary / 2) % 8 == 0 &&
+        aligned(q) && aligned(k) && aligned(v) && aligned(q_out) && aligned(k_pool) && aligned(v_pool) &&
+        row_stride % step == 0 && page_stride % step == 0 && head_stride % step == 0 &&
+        (v_first == nullptr || (aligned(v_first) && v_first_stride % step == 0));
+    if (pieces) {
+        int lanes = 1;
+        while (lanes * 8 < row) {
+            lanes *= 2;
+        }
+        const int groups = kThreads / lanes;
+        // few tokens: a block's groups take one head each (many small blocks); long steps: a block per token
+        const int heads_per_block = n_tokens >= 256 ? n_slots : groups;
+        const size_t smem = (static_cast<size_t>(rotary) + 32) * sizeof(float);
+        const dim3 grid(n_tokens, (n_slots + heads_per_block - 1) / heads_per_block);
+        PL_REQUIRE(grid.y <= 65535, "norm_rope_mix_write: too many heads (%d)", n_slots);
         PL_DISPATCH_DTYPE(dtype, "norm_rope_mix_write", {
-            if (row_smem > 48 * 1024) {
-                cudaFuncSetAttribute(norm_rope_mix_write_row_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(row_smem));
-            }
-            pl_launch_overlapped(norm_rope_mix_write_row_kernel<scalar_t>, dim3(n_tokens), dim3(kThreads), row_smem, stream,
-                                 static_cast<const scalar_t*>(q), row_stride, static_cast<const scalar_t*>(v_first),
+            pl_launch_overlapped(norm_rope_mix_write_pieces_kernel<scalar_t>, grid, dim3(kThreads), smem, stream,
+                                 static_cast<const scalar_t*>(q), static_cast<const scalar_t*>(k),
+                                 static_cast<const scalar_t*>(v), row_stride, static_cast<const scalar_t*>(v_first),
                                  v_first_stride, lambda, static_cast<scalar_t*>(q_out), pos, entry, table, table_width,
-                                 static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool), page_stride, head_stride,
-                                 page_size, n_pages, inv_freq, rotary, n_heads, n_kv, dim, vdim, row, mode, q_weight,
-                                 k_weight, eps, load_pieces, store_pieces, status);
+                                 static_cast<scalar_t*>(k_pool), static_cast<scalar_t*>(v_pool), page_stride,
+                                 head_stride, page_size, n_pages, inv_freq, rotary, n_heads, n_kv, dim, vdim, row,
+                                 heads_per_block, lanes, mode, q_weight, k_weight, eps, status);
         });
         PL_CHECK_LAUNCH("norm_rope_mix_write");
         return 0;
     }
-    // Else a warp takes a head at a time: a block of four warps gets four head slots in steps of few tokens (many
-    // small blocks fill the device) and eight in long steps (two a warp).
+    // Other sizes: a warp takes a head at a time, column by column; a block of four warps gets four head slots in
+    // steps of few tokens (many small blocks fill the device) and eight in long steps (two a warp).
     const int heads_per_block = n_tokens >= 256 ? 8 : 4;
     const size_t smem = (static_cast<size_t>(rotary) + 32 + static_cast<size_t>(kThreads / 32) * dim) * sizeof(float);
     PL_REQUIRE(smem <= 48 * 1024, "norm_rope_mix_write: a key size of %d is too large", dim);

@@ -283,9 +283,11 @@ def norm_rope_mix_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, v_fir
                         q_out: torch.Tensor, pos: torch.Tensor, entry: torch.Tensor, table: torch.Tensor,
                         k_pool: torch.Tensor, v_pool: torch.Tensor, page_size: int, inv_freq: torch.Tensor | None,
                         rotary: int, mode: str, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
-                        eps: float, status: torch.Tensor | None = None) -> None:
+                        eps: float, status: torch.Tensor | None = None, row_stride: int | None = None,
+                        v_first_stride: int | None = None) -> None:
     """q [T, nh, dim], k [T, nkv, dim], v [T, nkv, vdim] (slices of one projection's output: equal row
-    strides) are normed (mode: "none", "per_head" with weights fp32 [dim], "whole" over the whole projection with
+    strides; `row_stride`, and `v_first_stride` for v_first, name them where a step of one token would hide them:
+    the kernel chosen depends on them) are normed (mode: "none", "per_head" with weights fp32 [dim], "whole" over the whole projection with
     weights fp32 [nh * dim] and [nkv * dim], "unit_after": per head, no weights, after the rotation), rotated over
     the first `rotary` columns of every head (inv_freq fp64 [rotary / 2] or None), v mixed with v_first [T, nkv,
     vdim] as (1 - lam) v + lam v_first (None: not), and written: q to q_out [T, nh, row], k and v into the pools
@@ -302,11 +304,12 @@ def norm_rope_mix_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, v_fir
     assert q_out.shape == (tokens, n_heads, row) and q_out.is_contiguous() and q_out.dtype == q.dtype
     assert k_pool.shape == (n_pages, n_kv, page_size, row) == v_pool.shape and k_pool.dtype == q.dtype == v_pool.dtype
     assert k_pool.stride() == v_pool.stride() and k_pool.stride(3) == 1 and k_pool.stride(2) == row
-    v_first_stride = 0
     if v_first is not None:
         assert v_first.shape == v.shape and v_first.dtype == q.dtype and v_first.stride(2) == 1
         assert v_first.stride(1) == vdim
-        v_first_stride = v_first.stride(0)
+        v_first_stride = v_first.stride(0) if v_first_stride is None else int(v_first_stride)
+    else:
+        v_first_stride = 0
     n_q, n_k = (n_heads * dim, n_kv * dim) if mode == "whole" else (dim, dim)
     for w_, n_ in ((q_weight, n_q), (k_weight, n_k)):
         assert w_ is None or (w_.dtype == torch.float32 and w_.numel() == n_ and w_.is_contiguous())
@@ -314,7 +317,8 @@ def norm_rope_mix_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, v_fir
     assert pos.numel() == tokens and entry.numel() == tokens and table.dim() == 2 and table.is_contiguous()
     if inv_freq is not None:
         assert inv_freq.dtype == torch.float64 and inv_freq.numel() == rotary // 2 and inv_freq.is_contiguous()
-    _call("pl_norm_rope_mix_write", _p(q), _p(k), _p(v), q.stride(0), _p(v_first), v_first_stride, float(lam),
+    _call("pl_norm_rope_mix_write", _p(q), _p(k), _p(v), q.stride(0) if row_stride is None else int(row_stride),
+          _p(v_first), v_first_stride, float(lam),
           _p(q_out), _p(pos), _p(entry), _p(table), table.shape[1], _p(k_pool), _p(v_pool), k_pool.stride(0),
           k_pool.stride(1), page_size, n_pages, _p(inv_freq), int(rotary) if inv_freq is not None else 0, tokens,
           n_heads, n_kv, dim, vdim, row, NORM_MODES[mode], _p(q_weight), _p(k_weight), float(eps), _code(q.dtype),

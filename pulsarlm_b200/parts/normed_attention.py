@@ -185,18 +185,19 @@ class NormedAttention(Attention):
         k = proj[:, q_end:k_end].view(tokens, nkv, hd)
         v = proj[:, k_end:v_end].view(tokens, nkv, vd)
         gate = proj[:, v_end:v_end + nh] if self.gated else None
-        first = None
+        first, first_stride = None, None
         if self.value_mix == "source":
-            batch.extras[("values", self.value_stream)] = v
+            # (with the row stride of the product they are columns of: a view of one token forgets it)
+            batch.extras[("values", self.value_stream)] = (v, proj.stride(0))
         elif self.value_mix == "mix":
-            first = batch.extras.get(("values", self.value_stream))
+            first, first_stride = batch.extras.get(("values", self.value_stream), (None, None))
             if first is None:
                 raise RuntimeError(f"normed_attention: no layer before this one left values under {self.value_stream!r}")
         q_rows = torch.empty((tokens, nh, row), dtype=h.dtype, device=h.device)
         inv_freq, rotary = self.position.table()
         ops.norm_rope_mix_write(q, k, v, first, self.lam, q_rows, batch.pos, batch.entry, table, cache.k_pool,
                                 cache.v_pool, cache.page_size, inv_freq, rotary, self.qk_norm, self.q_weight,
-                                self.k_weight, self.norm_eps, batch.status)
+                                self.k_weight, self.norm_eps, batch.status, proj.stride(0), first_stride)
         out = torch.empty((tokens, nh, row), dtype=h.dtype, device=h.device)
         self.attend(q_rows, out, table, batch, gate=gate if self.head_gate else None)
         if self.gated and not self.head_gate:
