@@ -1094,37 +1094,44 @@ def puvirax_kernels(width: int, pk: dict) -> dict:
             scratch = torch.empty(ops.attention_decode_scratch_floats(batch, heads, hd, splits), device=dev)
             note(f"attention_decode_bias_b64_{name}_splits{splits}",
                  time_kernel(lambda: ops.attention_decode(q, kvp[0], kvp[1], table, pos, ent, res, page, window, 0.125, splits,
-                                                          scratch, extras=ops.attention_extras(q, None, None, True, 0.0, bias))),
+                                                          scratch, extras=ops.attention_extras(q, None, None, False, 0.0, bias))),
                  read)
-            note(f"attention_decode_gate_b64_{name}_splits{splits}",
+            note(f"attention_decode_bias_gate_b64_{name}_splits{splits}",
                  time_kernel(lambda: ops.attention_decode(q, kvp[0], kvp[1], table, pos, ent, res, page, window, 0.125, splits,
-                                                          scratch, extras=ops.attention_extras(q, None, gate, True))), read)
+                                                          scratch, extras=ops.attention_extras(q, None, gate, False, 0.0, bias))),
+                 read)
             note(f"attention_decode_b64_{name}_splits{splits} (Llama)",
                  time_kernel(lambda: ops.attention_decode(q, kvp[0], kvp[1], table, pos, ent, res, page, window, 0.125, splits,
                                                           scratch)), read)
-    # a 2,048-token prompt through the tiled kernel, with and without the bias and the gate
+    # a 2,048-token prompt through the tiled kernels: the bias inside (mma.sync, the build with extras), the gate after
+    # the plain kernel, and the Llama layer's tcgen05 kernel at the same shape (pages as the cache manager lays them out)
     tokens = 2048
     n_pages = tokens // page
     table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, n_pages)
     q = torch.randn((tokens, heads, hd), device=dev).to(bf)
     res = torch.empty_like(q)
-    kvp = torch.randn((2, n_pages, kv, page, hd), device=dev).to(bf)
+    kvp = torch.randn((n_pages, 2, kv, page, hd), device=dev).to(bf)
+    k_pool, v_pool = kvp[:, 0], kvp[:, 1]
     gate = torch.randn((tokens, heads), device=dev).to(bf)
     rows = ops.attention_prefill_tile_rows()
     tiles = torch.tensor([(r, min(rows, tokens - r), r, 0) for r in range(0, tokens, rows)], dtype=torch.int32, device=dev)
+    note("sigmoid_gate_heads_T2048 (the gate of a layer without a bias, after its attention)",
+         time_kernel(lambda: ops.sigmoid_gate_heads(res, gate)), tokens * heads * hd * 4)
     for window in (1024, None):
         flops = 4.0 * heads * hd * sum(min(p + 1, window or tokens) for p in range(tokens))
         name = f"w{window}" if window else "causal"
-        for what, ex in (("bias, split weights", ops.attention_extras(q, None, None, True, 0.0, bias)),
-                         ("gate, split weights", ops.attention_extras(q, None, gate, True)),
-                         ("split weights", ops.attention_extras(q, None, None, True)),
+        for what, ex in (("bias", ops.attention_extras(q, None, None, False, 0.0, bias)),
+                         ("bias, weights in two terms", ops.attention_extras(q, None, None, True, 0.0, bias)),
                          ("plain, mma.sync", None)):
-            ms = time_kernel(lambda: ops.attention_prefill(q, kvp[0], kvp[1], table, tiles, res, page, window, 0.125, extras=ex))
+            ms = time_kernel(lambda: ops.attention_prefill(q, k_pool, v_pool, table, tiles, res, page, window, 0.125, extras=ex))
             note(f"attention_prefill_T2048_{name} ({what})", ms, None, flops)
-        if ops.attention_prefill_tcgen05_supports(q, kvp[0], page):
-            ms = time_kernel(lambda: ops.attention_prefill_tcgen05(q, kvp[0], kvp[1], table, tiles, res, page, window, 0.125,
+        if ops.attention_prefill_tcgen05_supports(q, k_pool, page):
+            ms = time_kernel(lambda: ops.attention_prefill_tcgen05(q, k_pool, v_pool, table, tiles, res, page, window, 0.125,
                                                                    None, 1, None, False))
-            note(f"attention_prefill_T2048_{name} (tcgen05: Llama)", ms, None, flops)
+            note(f"attention_prefill_T2048_{name} (tcgen05: Llama, and the layers without a bias)", ms, None, flops)
+            ms = time_kernel(lambda: ops.attention_prefill_tcgen05(q, k_pool, v_pool, table, tiles, res, page, window, 0.125,
+                                                                   None, 1, None, False, distance_bias=bias))
+            note(f"attention_prefill_T2048_{name} (tcgen05 with the bias)", ms, None, flops)
     return out
 
 

@@ -78,6 +78,11 @@ struct TcPrefillParams {
     float* mass_part;            // zero before the launch
     int mass_pages;
     float scale;
+    // A bias by distance (the build with BIAS only): fp32 [n_heads, bias_rows], a head's entries side by
+    // side; bias[h, min(d, bias_rows - 1)] joins head h's scaled score of a key d tokens before the query.
+    const float* bias;
+    int bias_rows;
+    float inv_scale;  // the bias enters the raw products: bias / scale, so that (s + bias / scale) * scale is the biased score
 };
 
 // What pl_attention_prefill_tcgen05 needs to measure attention mass: the rows' weights,
@@ -140,7 +145,7 @@ __device__ __forceinline__ uint64_t smem_descriptor_mn(const void* tile, uint32_
 // WIDE (with HEADS == 2, for odd groups): the two "heads" of the CTA are the two
 // 128-row halves of one tile of up to 256 rows of ONE head: they share K and V just
 // the same, and everything that says head `hs` below means rows 128 hs ... of it.
-template <int HD, int HEADS, bool WIDE>
+template <int HD, int HEADS, bool WIDE, bool BIAS = false>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const TcPrefillParams p) {
@@ -503,6 +508,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 mbar_arrive(&s_free[hs][b]);
             }
             const int key0 = (j0 + j) * kKeys + part * kMyKeys;
+            if constexpr (BIAS) {
+                // this row's bias at every key's distance (neighbouring keys, neighbouring entries of the head's row)
+                const float* bias_row = p.bias + static_cast<int64_t>(head) * p.bias_rows;
+#pragma unroll
+                for (int c = 0; c < kMyKeys; ++c) {
+                    const int d = min(max(pos - (key0 + c), 0), p.bias_rows - 1);
+                    s[c] = fmaf(__ldg(bias_row + d), p.inv_scale, s[c]);
+                }
+            }
             const bool edge = (j0 + j) * kKeys + kKeys - 1 > pos0 ||
                 (p.window > 0 && (j0 + j) * kKeys < pos0 + kSpan - p.window);
             // The tile's maximum, on the raw products (the scale is positive), four running
@@ -820,13 +834,13 @@ __global__ void attention_mass_fold_prefill_kernel(const TcPrefillParams p, int 
     }
 }
 
-template <int HD, int HEADS, bool WIDE>
+template <int HD, int HEADS, bool WIDE, bool BIAS = false>
 int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcPrefillParams& p,
                       int n_tiles, int n_heads, cudaStream_t stream) {
     constexpr int smem = (HEADS == 2 ? 0 : kRows * HD * 2) + stages_kv(HEADS) * 2 * kKeys * HD * 2 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, HEADS, WIDE>,
+        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, HEADS, WIDE, BIAS>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (err != cudaSuccess) {
             return pl_fail(3, "attention_prefill_tcgen05: cannot set shared memory size: %s",
@@ -834,7 +848,7 @@ int launch_tc_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
         }
         configured = true;
     }
-    attention_prefill_tcgen05_kernel<HD, HEADS, WIDE>
+    attention_prefill_tcgen05_kernel<HD, HEADS, WIDE, BIAS>
         <<<dim3(WIDE ? n_heads : n_heads / HEADS, n_tiles, p.n_splits), kThreadsTc, smem, stream>>>(mq, mk, mv, p);
     PL_CHECK_LAUNCH("attention_prefill_tcgen05");
     if (p.n_splits > 1) {
@@ -872,12 +886,13 @@ PL_API int64_t pl_attention_prefill_scratch_floats(int n_tokens, int n_heads, in
 // `wide` (odd groups only; ignored for even ones): the tiles have up to 256 rows
 // (pl_attention_prefill_tcgen05_tile_rows), else up to 128. `mass` (optional): also
 // measures attention mass (see PlPrefillMass).
-PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int n_tokens, const void* k_pool,
-                                        const void* v_pool, int64_t page_stride, int64_t head_stride, int page_size,
-                                        int n_pages, const int32_t* table, int table_width, const int32_t* tiles,
-                                        int n_tiles, void* out, int64_t out_row_stride, int n_heads, int n_kv_heads,
-                                        int head_dim, int window, float scale, int n_splits, float* scratch,
-                                        int wide, const PlPrefillMass* mass, int32_t* status, cudaStream_t stream) {
+static int run_tc_prefill(const void* q, int64_t q_row_stride, int n_tokens, const void* k_pool,
+                          const void* v_pool, int64_t page_stride, int64_t head_stride, int page_size,
+                          int n_pages, const int32_t* table, int table_width, const int32_t* tiles,
+                          int n_tiles, void* out, int64_t out_row_stride, int n_heads, int n_kv_heads,
+                          int head_dim, int window, float scale, int n_splits, float* scratch,
+                          int wide, const PlPrefillMass* mass, const float* bias, int bias_rows, int32_t* status,
+                          cudaStream_t stream) {
     PL_REQUIRE(n_tiles >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_tokens > 0,
                "attention_prefill_tcgen05: bad sizes tiles=%d heads=%d kv_heads=%d tokens=%d", n_tiles, n_heads,
                n_kv_heads, n_tokens);
@@ -939,6 +954,14 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
     // a tile of up to 256 rows as two halves (`wide`), or of up to 128 rows with both
     // warpgroups on it.
     const bool pairs = p.group % 2 == 0;
+    p.bias = bias;
+    p.bias_rows = bias_rows;
+    p.inv_scale = 1.0f / scale;
+    if (bias != nullptr) {
+        PL_REQUIRE(pairs && mass == nullptr && bias_rows > 0,
+                   "attention_prefill_tcgen05: a bias by distance is taken with two heads of a kv head per CTA (an even "
+                   "group), without attention mass");
+    }
     p.query_weights = nullptr;
     p.mass_part = nullptr;
     p.mass_pages = 0;
@@ -960,7 +983,10 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
         p.mass_pages = mass->pages;
     }
     int code;
-    if (head_dim == 64) {
+    if (bias != nullptr) {
+        code = head_dim == 64 ? launch_tc_prefill<64, 2, false, true>(mq, mk, mv, p, n_tiles, n_heads, stream)
+                              : launch_tc_prefill<128, 2, false, true>(mq, mk, mv, p, n_tiles, n_heads, stream);
+    } else if (head_dim == 64) {
         code = pairs ? launch_tc_prefill<64, 2, false>(mq, mk, mv, p, n_tiles, n_heads, stream)
             : wide   ? launch_tc_prefill<64, 2, true>(mq, mk, mv, p, n_tiles, n_heads, stream)
                      : launch_tc_prefill<64, 1, false>(mq, mk, mv, p, n_tiles, n_heads, stream);
@@ -979,4 +1005,31 @@ PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int
         p, n_tiles, (!pairs && wide) ? 2 * kRows : kRows, mass->step_mass, mass->step_weight);
     PL_CHECK_LAUNCH("attention_mass_fold_prefill");
     return 0;
+}
+
+PL_API int pl_attention_prefill_tcgen05(const void* q, int64_t q_row_stride, int n_tokens, const void* k_pool,
+                                        const void* v_pool, int64_t page_stride, int64_t head_stride, int page_size,
+                                        int n_pages, const int32_t* table, int table_width, const int32_t* tiles,
+                                        int n_tiles, void* out, int64_t out_row_stride, int n_heads, int n_kv_heads,
+                                        int head_dim, int window, float scale, int n_splits, float* scratch,
+                                        int wide, const PlPrefillMass* mass, int32_t* status, cudaStream_t stream) {
+    return run_tc_prefill(q, q_row_stride, n_tokens, k_pool, v_pool, page_stride, head_stride, page_size, n_pages, table,
+                          table_width, tiles, n_tiles, out, out_row_stride, n_heads, n_kv_heads, head_dim, window, scale,
+                          n_splits, scratch, wide, mass, nullptr, 0, status, stream);
+}
+
+// The same with a bias by distance: bias fp32 [n_heads, bias_rows] (a head's entries side by side);
+// bias[h, min(d, bias_rows - 1)] joins head h's scaled score of a key d tokens before the query. Even GQA
+// groups only (two heads of a kv head per CTA); no attention mass.
+PL_API int pl_attention_prefill_tcgen05_bias(const void* q, int64_t q_row_stride, int n_tokens, const void* k_pool,
+                                             const void* v_pool, int64_t page_stride, int64_t head_stride,
+                                             int page_size, int n_pages, const int32_t* table, int table_width,
+                                             const int32_t* tiles, int n_tiles, void* out, int64_t out_row_stride,
+                                             int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                                             int n_splits, float* scratch, const float* bias, int bias_rows,
+                                             int32_t* status, cudaStream_t stream) {
+    PL_REQUIRE(bias != nullptr && bias_rows > 0, "attention_prefill_tcgen05_bias: needs a bias table");
+    return run_tc_prefill(q, q_row_stride, n_tokens, k_pool, v_pool, page_stride, head_stride, page_size, n_pages, table,
+                          table_width, tiles, n_tiles, out, out_row_stride, n_heads, n_kv_heads, head_dim, window, scale,
+                          n_splits, scratch, 0, nullptr, bias, bias_rows, status, stream);
 }

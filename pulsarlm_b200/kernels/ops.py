@@ -25,7 +25,7 @@ _PTR = ctypes.c_void_p
 _lib = None
 _lock = threading.Lock()
 
-ABI_VERSION = 27
+ABI_VERSION = 28
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -75,6 +75,8 @@ _SIGNATURES = {
     "pl_attention_prefill_supports": [_I32, _I32, _I32],
     "pl_attention_prefill_tcgen05": [_PTR, _I64, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32,
                                      _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _I32, _PTR, _PTR, _PTR],
+    "pl_attention_prefill_tcgen05_bias": [_PTR, _I64, _I32, _PTR, _PTR, _I64, _I64, _I32, _I32, _PTR, _I32, _PTR, _I32,
+                                          _PTR, _I64, _I32, _I32, _I32, _I32, _F32, _I32, _PTR, _PTR, _I32, _PTR, _PTR],
     "pl_attention_prefill_tcgen05_tile_rows": [_I32],
     "pl_attention_prefill_tcgen05_supports": [_I32, _I32, _I32, _I64, _I64, _I64, _I32],
     "pl_attention_prefill_tile_rows": [],
@@ -1266,8 +1268,9 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
                               tiles: torch.Tensor, out: torch.Tensor, page_size: int, window: int | None,
                               scale: float, status: torch.Tensor | None = None, n_splits: int = 1,
                               scratch: torch.Tensor | None = None, wide: bool = False,
-                              mass: tuple | None = None) -> None:
-    """As attention_prefill, on the tcgen05 tensor cores. With n_splits > 1 every tile's
+                              mass: tuple | None = None, distance_bias: torch.Tensor | None = None) -> None:
+    """As attention_prefill, on the tcgen05 tensor cores. `distance_bias` fp32 [nh, rows] (even GQA groups, no
+    wide tiles, no mass): entry min(distance, rows - 1) of a head's row joins its scaled scores. With n_splits > 1 every tile's
     keys are shared out over that many CTAs and merged through `scratch` (float32,
     attention_prefill_scratch_floats elements): for few tiles over many keys. `wide`: the
     tiles have up to attention_prefill_tcgen05_tile_rows(group) rows instead of 128.
@@ -1301,6 +1304,16 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     assert k_pool.stride() == v_pool.stride() and k_pool.stride(3) == 1 and k_pool.stride(2) == head_dim
     assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
     assert tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 4 and tiles.is_contiguous()
+    if distance_bias is not None:
+        _dev(distance_bias)
+        assert mass is None and not wide and (n_heads // n_kv) % 2 == 0
+        assert distance_bias.dtype == torch.float32 and distance_bias.is_contiguous()
+        assert distance_bias.dim() == 2 and distance_bias.shape[0] == n_heads and distance_bias.shape[1] > 0
+        _call("pl_attention_prefill_tcgen05_bias", _p(q), q.stride(0), tokens, _p(k_pool), _p(v_pool), k_pool.stride(0),
+              k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(tiles), tiles.shape[0], _p(out),
+              out.stride(0), n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch),
+              _p(distance_bias), distance_bias.shape[1], _p(status), _stream())
+        return
     _call("pl_attention_prefill_tcgen05", _p(q), q.stride(0), tokens, _p(k_pool), _p(v_pool), k_pool.stride(0),
           k_pool.stride(1), page_size, n_pages, _p(table), table.shape[1], _p(tiles), tiles.shape[0], _p(out),
           out.stride(0), n_heads, n_kv, head_dim, int(window or 0), float(scale), int(n_splits), _p(scratch),

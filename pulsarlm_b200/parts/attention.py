@@ -543,6 +543,12 @@ class Attention(Part):
             plan["tiles_wide"] = np.array(wide_tiles, dtype=np.int32).reshape(len(wide_tiles), 4)
         return plan
 
+    def _bias_alone(self, gate) -> bool:
+        """Whether the layer's only extra is a bias by distance, its softmax weights go in one bfloat16 term and its
+        heads come in pairs per kv head: what the tcgen05 prompt kernel's build with a bias takes."""
+        return (self.distance_bias is not None and gate is None and self.sinks is None and not self.softcap
+                and not self.split_weights and (self.n_heads // self.n_kv) % 2 == 0)
+
     def _attend_with_extras(self, q, out, table, batch, plan, decode_kernel: bool, prefill_kernel: bool,
                             gate: torch.Tensor | None = None) -> None:
         """Attention with a score cap, a sink term, a bias by distance and / or a gate per head
@@ -577,6 +583,25 @@ class Attention(Part):
         tiles = plan.get("tiles")
         if prefill_kernel and tiles is not None and n_decode == int(batch.n_decode):
             # (the tile list covers exactly the tokens after the leading single tokens)
+            if self._bias_alone(gate):
+                # A bias by distance and nothing else: the tcgen05 kernel's build that adds it to its products.
+                if self._prefill_tcgen05 is None:
+                    self._prefill_tcgen05 = ops.attention_prefill_tcgen05_supports(q, cache.k_pool, cache.page_size)
+                if self._prefill_tcgen05:
+                    ctas = tiles.shape[0] * (self.n_heads // 2)
+                    max_keys = int(plan.get("max_keys") or 0)
+                    if self.window:
+                        max_keys = min(max_keys, self.window + ops.attention_prefill_tile_rows())
+                    splits = prefill_splits(ctas, max_keys, tokens - n_decode, self.n_heads, self.head_dim, q.device)
+                    scratch = None
+                    if splits > 1:
+                        scratch = torch.empty(ops.attention_prefill_scratch_floats(tokens, self.n_heads, self.head_dim,
+                                                                                   splits),
+                                              dtype=torch.float32, device=q.device)
+                    ops.attention_prefill_tcgen05(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size,
+                                                  self.window, self.scale, batch.status, splits, scratch, False,
+                                                  distance_bias=bias)
+                    return
             ops.attention_prefill(q, cache.k_pool, cache.v_pool, table, tiles, out, cache.page_size, self.window,
                                   self.scale, batch.status,
                                   extras=ops.attention_extras(q, self.sinks, gate, self.split_weights, self.softcap,

@@ -233,7 +233,7 @@ def test_attention_with_a_bias_by_distance_at_window_edges(window, spike, rows, 
         assert plain.relative_error_of(out.cpu(), want) < (1e-5 if dtype == torch.float32 else 1e-2), (dtype, window, spike)
 
 
-@pytest.mark.parametrize("dim,heads,kv", [(32, 6, 2), (96, 4, 1), (64, 3, 3), (48, 8, 1)])
+@pytest.mark.parametrize("dim,heads,kv", [(32, 6, 2), (96, 4, 1), (64, 3, 3), (48, 8, 1), (64, 4, 2), (128, 8, 1)])
 @pytest.mark.parametrize("window,distance", [(None, None), (None, 150), (24, 23), (24, 24), (37, 36), (37, 37), (16, 15)])
 @pytest.mark.parametrize("rows,far", [(12, 40.0), (32, 64.0)])
 def test_tensor_core_attention_takes_the_bias_and_the_gate(dim, heads, kv, window, distance, rows, far):
@@ -253,9 +253,13 @@ def test_tensor_core_attention_takes_the_bias_and_the_gate(dim, heads, kv, windo
         table, keys, values, q_full, rel, k_pool, v_pool = _attention_case(gen, lengths, heads, kv, dim, page, dtype, rows,
                                                                           far, distance, queries)
         gate = torch.randn(len(queries), heads, generator=gen).to(dtype)
-        want = _attention_wanted(keys, values, q_full, rel, far, scale, window, queries) * torch.sigmoid(gate.double())[:, :, None]
+        plain_want = _attention_wanted(keys, values, q_full, rel, far, scale, window, queries)
+        want = plain_want * torch.sigmoid(gate.double())[:, :, None]
         q = torch.stack([q_full[e][p] for e, p in queries]).to(DEV)
+        ungated.append(plain_want)
         return q, k_pool, v_pool, table.to(DEV), gate.to(DEV), bias_by_distance(rel.to(DEV), far), want
+
+    ungated: list = []
 
     queries = [(e, n - 1) for e, n in enumerate(lengths)] + [(0, 0), (0, 1), (3, 64)]
     q, k_pool, v_pool, table, gate, bias, want = case(queries, 21)
@@ -280,6 +284,20 @@ def test_tensor_core_attention_takes_the_bias_and_the_gate(dim, heads, kv, windo
     ops.attention_prefill(q, k_pool, v_pool, table, _i32(tiles), out, page, window, scale,
                           extras=ops.attention_extras(q, None, gate, True, 0.0, bias))
     assert plain.relative_error_of(out.cpu(), want) < 1e-2, "prompt rows"
+    # the tcgen05 kernel's build with a bias (keys and values of a page side by side, heads in pairs per kv head)
+    both = torch.stack([k_pool, v_pool], dim=1).contiguous()
+    if (heads // kv) % 2 == 0 and ops.attention_prefill_tcgen05_supports(q, both[:, 0], page):
+        out = torch.empty_like(q)
+        ops.attention_prefill_tcgen05(q, both[:, 0], both[:, 1], table, _i32(tiles), out, page, window, scale,
+                                      distance_bias=bias)
+        assert plain.relative_error_of(out.cpu(), ungated[-1]) < 1e-2, "prompt rows on tcgen05"
+        for splits in (2, 3):
+            scratch = torch.empty(ops.attention_prefill_scratch_floats(q.shape[0], heads, dim, splits), dtype=torch.float32,
+                                  device=DEV)
+            out = torch.empty_like(q)
+            ops.attention_prefill_tcgen05(q, both[:, 0], both[:, 1], table, _i32(tiles), out, page, window, scale, None,
+                                          splits, scratch, distance_bias=bias)
+            assert plain.relative_error_of(out.cpu(), ungated[-1]) < 1e-2, ("prompt rows on tcgen05", splits)
 
 
 @pytest.mark.parametrize("experts,top,groups", [(8, 2, (4, 2)), (16, 3, (4, 3)), (6, 2, (3, 2)), (5, 1, None), (12, 4, (3, 1)),
