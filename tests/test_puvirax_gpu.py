@@ -93,7 +93,7 @@ def test_norms_rotation_and_value_mixing_on_the_way_to_the_cache(mode, heads, kv
     gen = torch.Generator().manual_seed(heads * 100 + dim)
     eps, lam, page = 1e-5, 0.3, 8
     row = -(-max(dim, vdim) // 16) * 16
-    rot = {"base": 100.0, "dims": rotary, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 32}}
+    rot = {"base": 100.0, "dims": rotary, "scaling": {"factor": 2.0, "low": 1.0, "high": 3.0, "original": 32}}
     inv_freq = plain.banded_frequencies(rot).to(DEV) if rotary else None
     for lengths, starts, spare in (([5, 3], [9, 0], 3), ([70, 33], [3, 20], 3), ([300, 40], [7, 0], 8), ([260], [0], 5)):
         tokens = sum(lengths)
@@ -641,15 +641,15 @@ def _random_config(seed: int):
         scale = pick([0.1, 0.3, dim ** -0.5, 2.0 * dim ** -0.5])
         if kind == "attention":
             layers.append(pt.rotary_layer(heads, kv, dim, vdim, pick([None, 0, 2, dim // 2, dim]), mlp, v_mix=v_mix, scale=scale,
-                                          base=pick([50.0, 10000.0, 500000.0]),
-                                          bands=pick([None, (4.0, 1.0, 4.0, 32), (8.0, 0.5, 2.0, 64)])))
+                                          base=pick([50.0, 10000.0, 1000000.0]),
+                                          bands=pick([None, (4.0, 0.5, 3.0, 32), (8.0, 0.5, 2.0, 64)])))
         else:
             window = pick([1, 2, 5, 16, 17, 31, 33, 50]) if kind == "attention_2" else None
             rows = pick([2, 4, 6, 12, 16, 32])
             layers.append(pt.biased_layer(kind, heads, kv, dim, vdim, rows, rows // 2 * pick([1.5, 4, 20.5]) + 1, mlp,
                                           window=window, v_mix=v_mix, scale=scale))
     return pt._config(pick([64, 101, 257]), width, pick([1e-6, 1e-5, 1e-3]), pick([1.0, 0.5, 3.0]),
-                      (pick([1, 17, 1021]), pick([1, 127, 100003]), pick([1, 7, 65537])), layers)
+                      (pick([1, 17, 2039]), pick([1, 211, 100003]), pick([1, 13, 65537])), layers)
 
 
 @pytest.mark.parametrize("seed", list(range(12)))
