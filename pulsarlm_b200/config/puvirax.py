@@ -194,8 +194,8 @@ class PuviraxConfig:
                                        bool(mixer.get("v_mix", False)), window, base, dims, scaling, bias_max,
                                        bias_rows, _feed_forward(entry, i)))
         mixing = [layer for layer in layers if layer.v_mix]
-        if any((layer.kv_heads, layer.value_dim) != (mixing[0].kv_heads, mixing[0].value_dim) for layer in mixing):
-            raise ConfigError("config.json: layers with v_mix must agree in kv_heads and vdim (they share values)")
+        if any(layer.kv_heads * layer.value_dim != mixing[0].kv_heads * mixing[0].value_dim for layer in mixing):
+            raise ConfigError("config.json: layers with v_mix must agree in kv_heads x vdim (they share a token's values)")
         pairs = None
         embedding = text.get("embedding")
         if isinstance(embedding, dict) and isinstance(embedding.get("bigram"), dict):

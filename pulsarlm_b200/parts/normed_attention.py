@@ -188,11 +188,15 @@ class NormedAttention(Attention):
         first, first_stride = None, None
         if self.value_mix == "source":
             # (with the row stride of the product they are columns of: a view of one token forgets it)
-            batch.extras[("values", self.value_stream)] = (v, proj.stride(0))
+            batch.extras[("values", self.value_stream)] = (proj[:, k_end:v_end], proj.stride(0))
         elif self.value_mix == "mix":
             first, first_stride = batch.extras.get(("values", self.value_stream), (None, None))
             if first is None:
                 raise RuntimeError(f"normed_attention: no layer before this one left values under {self.value_stream!r}")
+            if first.shape[1] != nkv * vd:
+                raise ValueError(f"normed_attention: the values under {self.value_stream!r} are {first.shape[1]} wide, "
+                                 f"this layer's {nkv * vd}")
+            first = first.view(tokens, nkv, vd)  # (a token's values as one row: the heads' split is each layer's own)
         q_rows = torch.empty((tokens, nh, row), dtype=h.dtype, device=h.device)
         inv_freq, rotary = self.position.table()
         ops.norm_rope_mix_write(q, k, v, first, self.lam, q_rows, batch.pos, batch.entry, table, cache.k_pool,

@@ -51,7 +51,7 @@ def test_bad_configurations_are_refused():
                    lambda t: t["layers"][1]["mixer"].update(kv_heads=3),
                    lambda t: t["layers"][1]["mixer"]["rot"].update(dims=7),
                    lambda t: t["layers"][0]["mixer"].pop("bias_max"),
-                   lambda t: t["layers"][2]["mixer"].update(vdim=8),           # (layers that mix values must agree)
+                   lambda t: t["layers"][2]["mixer"].update(vdim=8),           # (layers that mix values must agree in kv_heads x vdim)
                    lambda t: t["layers"][0]["mlp"]["router"].update(top=5),
                    lambda t: t["layers"][0]["mlp"]["router"]["groups"].update(count=3),
                    lambda t: t.pop("vocab")):

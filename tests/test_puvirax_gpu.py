@@ -606,6 +606,33 @@ def test_sizes_come_from_the_configuration():
         tm.check(tokens, harness.replay(tm.runner(8), steps), "sizes of one")
 
 
+def test_odd_sizes_and_a_larger_model():
+    """A width that is no multiple of four with key and value sizes that are no multiples of eight (every kernel's
+    plain form), and a model of wider rows (keys of 128, 112 and 80 beside values of 96, 48 and 24; layers that mix
+    values with different head splits of the same row), under prompts, a second request and single tokens."""
+    small = pt._config(101, 70, 1e-5, 1.3, (37, 5, 3), [
+        pt.biased_layer("attention_3", 3, 3, 10, 6, 7, 33.5, pt.routed(30, 7, 3, None, 18)),
+        pt.rotary_layer(6, 3, 14, 6, 6, pt.dense(50), base=77.0, bands=(3.0, 0.5, 2.5, 20)),
+        pt.biased_layer("attention_2", 9, 3, 22, 6, 5, 11, pt.routed(10, 9, 4, (3, 2)), window=13),
+        pt.rotary_layer(3, 1, 18, 30, 18, None, v_mix=False)])
+    large = pt._config(300, 200, 1e-6, 2.5, (509, 97, 11), [
+        pt.rotary_layer(8, 2, 80, 48, 40, pt.routed(48, 12, 4, (3, 2), 72), bands=(4.0, 1.0, 2.0, 256)),
+        pt.biased_layer("attention_2", 8, 4, 64, 24, 24, 300, pt.dense(352), window=200),
+        pt.biased_layer("attention_3", 4, 2, 128, 96, 20, 90, pt.dense(352), v_mix=False),
+        pt.biased_layer("attention_3", 8, 2, 48, 48, 16, 150, pt.routed(64, 8, 2, (4, 3), 40)),
+        pt.rotary_layer(6, 2, 112, 48, 112, pt.dense(100))])
+    for (cfg, rows), length in ((small, 120), (large, 450)):
+        for dtype in ("float32", "bfloat16"):
+            tm = pt.TinyPuvirax("-", dtype, cfg=cfg, rows=rows, seed=3)
+            tokens = {"p": pt.random_tokens(cfg, length, 50), "q": pt.random_tokens(cfg, 77, 51)}
+            p, q, cut = tokens["p"], tokens["q"], length - 40
+            steps = [([("p", p[:cut], list(range(0, cut, 7)))], []),
+                     ([("q", q[:70], [0, 69]), ("p", p[cut: cut + 1], [0])], [])]
+            steps += [([("p", [p[i]], [0])] + ([("q", [q[70 + i - cut - 1]], [0])] if i - cut - 1 < 7 else []), [])
+                      for i in range(cut + 1, length)]
+            tm.check(tokens, harness.replay(tm.runner(64), steps), "odd sizes and a larger model")
+
+
 def _random_config(seed: int):
     """Sizes, constants and layer order drawn at random: widths that are no multiple of 8, odd head counts, key and
     value sizes with and without a tensor-core kernel, windows from 1 up, bias tables of any height and reach, layers
@@ -621,8 +648,8 @@ def _random_config(seed: int):
     for _ in range(pick([2, 3, 4, 5, 6])):
         kind = pick(["attention", "attention_2", "attention_3"])
         v_mix = pick([True, True, False])
-        kv = mix_kv if v_mix else pick([1, 2, 3])
-        vdim = mix_vdim if v_mix else pick([4, 8, 24, 64])
+        # (layers that mix values agree in kv_heads x vdim, not in how the heads split it)
+        kv, vdim = pick([(mix_kv, mix_vdim), (1, mix_kv * mix_vdim)]) if v_mix else (pick([1, 2, 3]), pick([4, 8, 24, 64]))
         heads = kv * pick([1, 2, 3, 4])
         dim = pick([8, 12, 16, 24, 32, 64])
         choice = pick(["none", "dense", "dense", "moe", "moe"])
