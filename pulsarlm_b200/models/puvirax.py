@@ -52,10 +52,12 @@ def describe_puvirax(cfg: PuviraxConfig) -> ModelSpec:
             params["bias_far"] = layer.bias_max
             params["bias_rows"] = layer.bias_rows
             names.update(q_norm=m + "q.norm", k_norm=m + "k.norm", distance_bias=m + "rel")
+        names["value_mix"] = m + "vmix"   # (read by the layers that mix; the others may store one and ignore it)
         if layer.v_mix:
             params["value_stream"] = VALUE_STREAM
             params["value_mix"] = "source" if i == first_mixing else "mix"
-            names["value_mix"] = m + "vmix"
+        if layer.mlp is None:
+            names["ignored"] = {p + "norm2": (width,)}  # (a layer without feed-forward may still store its norm)
         mixer = PartSpec("normed_attention", params, names)
         norms = {"mixer": norm(p + "norm1")}
         feed_forward = None

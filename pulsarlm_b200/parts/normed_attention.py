@@ -78,7 +78,9 @@ class NormedAttention(Attention):
     128, work lists for many single tokens) and multiplies by the gate in a small kernel afterwards.
 
     params: hidden_size, n_heads, n_kv_heads, head_dim (dim), value_dim, scale, window, norm_eps,
-    qk_norm, position, bias_far, bias_rows (optional), value_mix, value_stream, head_gate."""
+    qk_norm, position, bias_far, bias_rows (optional), value_mix, value_stream, head_gate. tensors: q, k, v, o,
+    q_norm, k_norm, distance_bias, value_mix, gate, and `ignored`: {name: shape} of tensors that a checkpoint may
+    hold for the layer and nothing reads."""
 
     def __init__(self, spec: PartSpec, ctx: BuildContext):
         p = spec.params
@@ -124,9 +126,13 @@ class NormedAttention(Attention):
             needs[t["gate"]] = TensorNeed((nh, h))
         if p.get("value_mix") == "mix":
             needs[t["value_mix"]] = TensorNeed((), role="offset")
-        elif p.get("value_mix") == "source" and t.get("value_mix"):
-            # (the layer whose values the others mix in stores a factor too, and does not use it)
+        elif t.get("value_mix"):
+            # (the layer whose values the others mix in may store a factor too, and so may a layer that mixes
+            # nothing: neither uses it)
             needs[t["value_mix"]] = TensorNeed((), role="ignored", optional=True)
+        for name, shape in (t.get("ignored") or {}).items():
+            # (tensors a checkpoint may hold for this layer that nothing reads)
+            needs[name] = TensorNeed(tuple(shape), role="ignored", optional=True)
         return needs
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:

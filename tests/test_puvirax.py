@@ -96,3 +96,19 @@ def test_plain_implementation_is_causal_and_its_pieces_fit():
     h, router = torch.randn(5, 16).double(), torch.randn(8, 16).double()
     ids, w = plain.route(h, router, torch.full((8,), -5.0).double(), r)
     assert all(int(a) // 2 == int(b) // 2 for a, b in ids.tolist()) and bool((w > 0).all())
+
+
+def test_stored_but_unused_tensors_are_allowed_and_others_are_not():
+    """A layer without feed-forward may store its second norm, and a layer that mixes nothing a mixing factor: they
+    load (nothing reads them). A tensor the design has no place for is still an error."""
+    from pulsarlm_b200.weights.loader import WeightsError, check_names
+
+    (text, rows), _ = pt.CONFIGS["B"]   # (its last layer has no feed-forward and mixes nothing)
+    arch, cfg = read_model_config(text)
+    needs = tensor_needs_of(arch.describe(cfg))
+    shapes = pt.tensor_shapes(text, rows)
+    shapes.update({"l3.norm2": (text["width"],), "l3.mix.vmix": (), "l0.mix.vmix": ()})
+    check_names("a folder", needs, shapes)
+    shapes["l3.mix.g"] = (5, text["width"])
+    with pytest.raises(WeightsError):
+        check_names("a folder", needs, shapes)
