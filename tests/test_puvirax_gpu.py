@@ -621,7 +621,11 @@ def test_odd_sizes_and_a_larger_model():
         pt.biased_layer("attention_3", 4, 2, 128, 96, 20, 90, pt.dense(352), v_mix=False),
         pt.biased_layer("attention_3", 8, 2, 48, 48, 16, 150, pt.routed(64, 8, 2, (4, 3), 40)),
         pt.rotary_layer(6, 2, 112, 48, 112, pt.dense(100))])
-    for (cfg, rows), length in ((small, 120), (large, 450)):
+    # rows wider than the tensor-core kernels take (144 and 160): bias, window and gate on the CUDA-core kernel in both dtypes
+    wide = pt._config(90, 48, 1e-5, 1.0, (11, 2, 9), [
+        pt.rotary_layer(2, 1, 160, 40, 64, pt.dense(64), scale=0.1),
+        pt.biased_layer("attention_2", 4, 2, 136, 20, 8, 50, None, window=30, scale=0.1)])
+    for (cfg, rows), length in ((small, 120), (large, 450), (wide, 100)):
         for dtype in ("float32", "bfloat16"):
             tm = pt.TinyPuvirax("-", dtype, cfg=cfg, rows=rows, seed=3)
             tokens = {"p": pt.random_tokens(cfg, length, 50), "q": pt.random_tokens(cfg, 77, 51)}
